@@ -47,6 +47,8 @@ class Model:
     # -- loading -----------------------------------------------------------
     @staticmethod
     def _context(n_ctx: int, trained: int) -> int:
+        if trained is None:          # the configuration sets no limit
+            return n_ctx or DEFAULT_CTX
         return min(n_ctx, trained) if n_ctx else min(trained, DEFAULT_CTX)
 
     @classmethod
@@ -56,7 +58,7 @@ class Model:
         reference: 0 = min(trained context, 4096), else min(n_ctx, trained context)."""
         from .config import load_config
         t0 = time.time()
-        trained = load_config(path).max_positions or DEFAULT_CTX
+        trained = load_config(path).max_positions
         ctx = cls._context(n_ctx, trained)
         decoder = load_model_dir(path, resolve_dtype(dtype), device, max_positions=ctx)
         m = cls(decoder, ctx, max_batch, max_tokens)
@@ -71,7 +73,7 @@ class Model:
         t0 = time.time()
         if isinstance(config, dict):
             config = config_from_dict(config)
-        ctx = cls._context(n_ctx, config.max_positions or DEFAULT_CTX)
+        ctx = cls._context(n_ctx, config.max_positions)
         decoder = random_model(config, seed, resolve_dtype(dtype), device, max_positions=ctx)
         m = cls(decoder, ctx, max_batch, max_tokens)
         m.load_seconds = time.time() - t0

@@ -32,7 +32,7 @@ PAGE_SIZE = 64
 class KVLayerView:
     """What an attention mixer gets: its entry's pages and the step's block table."""
     k: torch.Tensor            # [n_pages, K, PAGE_SIZE, D]
-    v: torch.Tensor
+    v: torch.Tensor | None     # None for a group that keeps one row per token only (`KVSpec.values` off)
     block_table: torch.Tensor  # int32 [B, W]: page of position p of batch row b at [b, p // PAGE_SIZE]
     group: "KVGroup"
 
@@ -49,13 +49,14 @@ class KVGroup:
         self.spec, self.n_entries, self.n_pages = spec, n_entries, int(n_pages)
         shape = (n_entries, self.n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if spec.values else None
         self.pages = IdPool(self.n_pages, "cache page")
         self.page_lists: dict[int, list[int]] = {}   # slot -> page of each page index (-1: given back)
 
     @property
     def bytes_per_token(self) -> int:
-        return 2 * self.n_entries * self.spec.n_kv_heads * self.spec.head_dim * self.k.element_size()
+        return ((2 if self.spec.values else 1) * self.n_entries * self.spec.n_kv_heads * self.spec.head_dim
+                * self.k.element_size())
 
     def open(self, slot: int) -> None:
         self.page_lists[slot] = []
@@ -240,7 +241,7 @@ class SequenceCache:
         kind, g, j = place
         if kind == "kv":
             grp = self.kv_groups[g]
-            return KVLayerView(grp.k[j], grp.v[j], block_tables[g], grp)
+            return KVLayerView(grp.k[j], grp.v[j] if grp.v is not None else None, block_tables[g], grp)
         grp = self.state_groups[g]
         return StateLayerView(grp.state[j], grp)
 
@@ -257,7 +258,7 @@ class SequenceCache:
             assert set(g.page_lists) == set(self.lengths)
 
     def describe(self) -> str:
-        kv = sum(g.k.numel() * g.k.element_size() * 2 for g in self.kv_groups)
+        kv = sum(g.k.numel() * g.k.element_size() * (2 if g.v is not None else 1) for g in self.kv_groups)
         st = sum(g.state.numel() * g.state.element_size() for g in self.state_groups)
         return (f"cache: {self.n_pages} pages of {PAGE_SIZE} tokens in {len(self.kv_groups)} key/value group(s) "
                 f"({kv / 2**20:.1f} MiB), {len(self.state_groups)} state group(s) ({st / 2**20:.1f} MiB), "

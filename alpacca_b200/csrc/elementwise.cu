@@ -247,6 +247,30 @@ AB_API int ab_add_rmsnorm(float* residual, const void* delta, const float* weigh
 }
 
 // ---------------------------------------------------------------------------
+// residual += delta (float32 sum; delta float or bfloat16): the add alone, for a stream that takes two
+// sub-layers' outputs before its next norm
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ residual, const T* __restrict__ delta, size_t total) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) residual[i] += to_f32(delta[i]);
+}
+
+AB_API int ab_residual_add(float* residual, const void* delta, int dtype, long long total, cudaStream_t stream) {
+  if (total <= 0) return AB_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == AB_F32)
+    ab_launch(residual_add_kernel<float>, blocks, 256, 0, stream, residual, (const float*)delta, (size_t)total);
+  else if (dtype == AB_BF16)
+    ab_launch(residual_add_kernel<bf16>, blocks, 256, 0, stream, residual, (const bf16*)delta, (size_t)total);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
+}
+
+// ---------------------------------------------------------------------------
 // y[t, j] += bias[j]
 // ---------------------------------------------------------------------------
 template <typename T>

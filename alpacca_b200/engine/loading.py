@@ -35,7 +35,9 @@ def build_model(config: ModelConfig | dict, dtype=torch.bfloat16, device="cuda",
     if isinstance(config, dict):
         config = config_from_dict(config)
     arch = get_architecture(config.architecture)
-    limit = config.max_positions or DEFAULT_MAX_POSITIONS
+    limit = config.max_positions      # None: the configuration sets no limit, the caller's count stands
+    if limit is None:
+        limit = int(max_positions) if max_positions else DEFAULT_MAX_POSITIONS
     opts = BuildOptions(dtype=resolve_dtype(dtype), device=device,
                         max_positions=min(int(max_positions), limit) if max_positions else limit)
     return DecoderModel(arch.build(config, opts), opts, config)

@@ -204,6 +204,19 @@ def add_rmsnorm(residual, delta, weight, eps, out, rows=None, n_rows=None):
     return out
 
 
+def residual_add(residual, delta, n_rows=None):
+    """residual[:n] += delta[:n] in float32 (delta float32 or bfloat16, the same width)."""
+    _cuda(residual, delta)
+    E = residual.shape[-1]
+    n = residual.numel() // E if n_rows is None else n_rows
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and delta.is_contiguous()
+          and delta.shape[-1] == E and residual.numel() >= n * E and delta.numel() >= n * E,
+          "residual_add: residual float32 [T,E], delta [T,E]")
+    _check(_lib("elementwise").ab_residual_add(_p(residual), _p(delta), _dt(delta), ctypes.c_longlong(n * E), _stream()),
+           "residual_add")
+    return residual
+
+
 def add_bias(y, bias):
     """y[t,j] += bias[j] in place; bias float32."""
     _cuda(y, bias)
@@ -906,3 +919,172 @@ def attention_tc_status() -> int:
 def attention_stream_status() -> int:
     """0, or the code left by a streamed decode attention kernel that gave up waiting on a barrier (synchronises)."""
     return _lib("attention_stream").ab_attention_stream_status()
+
+
+# ---------------------------------------------------------------------------
+# the matrix-memory recurrence, attention over a cached latent, routed experts
+
+def mlstm_state_row(D: int, V: int) -> int:
+    """Floats that one (sequence, head) of the matrix memory keeps: S [D, V], n [D], m, padded to 16 bytes."""
+    return (D * V + D + 1 + 3) & ~3
+
+
+def mlstm_step(proj, offsets, bias_i, bias_f, state, ctx, H, D, V, cap, qscale, norm_weight, eps, out,
+               write_state=True):
+    """The matrix-memory recurrence over the step's tokens, from each sequence's state to its new state.
+
+    proj float32 [T, N]: one row per token with q | k | v | g | zi | zf at `offsets` (six column offsets);
+    state float32 [slots, H, mlstm_state_row(D, V)]; out [T, H*V] of the activation dtype gets
+    o / rms(o per head) * norm_weight * sigmoid(g).  Sequences, slots and padding rows are taken from the
+    context's device arrays (cu_q, slots, tok_seq)."""
+    _cuda(proj, bias_i, bias_f, state, norm_weight, out)
+    T, B = ctx.n_tokens, ctx.n_seqs
+    off_q, off_k, off_v, off_g, off_i, off_f = (int(o) for o in offsets)
+    ld = proj.shape[-1]
+    _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.numel() >= T * ld,
+          "mlstm_step: proj must be contiguous float32 [T, N]")
+    _need(max(off_q + H * D, off_k + H * D, off_v + H * V, off_g + H * V, off_i + H, off_f + H) <= ld,
+          "mlstm_step: an offset reaches beyond the projected row")
+    row = mlstm_state_row(D, V)
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, row),
+          f"mlstm_step: state must be contiguous float32 [slots, {H}, {row}]")
+    for b in (bias_i, bias_f):
+        _need(b.dtype == torch.float32 and b.numel() == H and b.is_contiguous(), "mlstm_step: gate biases float32 [H]")
+    _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == H * V and norm_weight.is_contiguous(),
+          "mlstm_step: norm weight float32 [H*V]")
+    _need(out.is_contiguous() and out.shape[-1] == H * V and out.numel() >= T * H * V, "mlstm_step: out [T, H*V]")
+    _i32(ctx.cu_q, B + 1, "cu_q")
+    _i32(ctx.slots, B, "slots")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    coef = torch.empty((T, H, 3), dtype=torch.float32, device=proj.device)
+    o_raw = torch.empty((T, H, V), dtype=torch.float32, device=proj.device)
+    _check(_lib("mlstm").ab_mlstm_step(
+        _p(proj), ld, off_q, off_k, off_v, off_g, off_i, off_f, _p(bias_i), _p(bias_f), _p(state), row, H, D, V,
+        _p(ctx.cu_q), _p(ctx.slots), _p(ctx.tok_seq), B, T, ctypes.c_float(cap), ctypes.c_float(qscale), _p(coef),
+        _p(o_raw), _p(norm_weight), ctypes.c_float(eps), _p(out), _dt(out), 1 if write_state else 0, _stream()),
+        "mlstm_step")
+    return out
+
+
+def latent_prep(x, Q, C, R, q_norm_weight, c_norm_weight, eps, rot, ctx, cache, cq_out, write_cache=True):
+    """Per token of x float32 [T, Q + C + R]: cq_out = rmsnorm(x[:Q]) * q_norm_weight; the page row of the
+    token's position gets [rmsnorm(x[Q:Q+C]) * c_norm_weight | x[Q+C:] rotated by position].
+    `rot` = (cos, sin, n_rot, pairing) with pairing 0 (pairs (2i, 2i+1)), or None.  `cache.k`: pages
+    [n_pages, 1, page, C + R] of the activation dtype."""
+    pages, table = cache.k, cache.block_table
+    cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
+    _cuda(x, q_norm_weight, c_norm_weight, cos, sin, pages, table, cq_out)
+    T = ctx.n_tokens
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[-1] >= Q + C + R and x.numel() >= T * x.shape[-1],
+          "latent_prep: x must be contiguous float32 [T, Q + C + R]")
+    _need(pairing == 0, "latent_prep rotates pairs (2i, 2i+1) only")
+    _need(n_rot <= R, f"latent_prep: {n_rot} rotated dims, the rotated part has {R}")
+    for wt, n in ((q_norm_weight, Q), (c_norm_weight, C)):
+        _need(wt.dtype == torch.float32 and wt.numel() == n and wt.is_contiguous(), "latent_prep: norm weights float32")
+    if n_rot:
+        _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+              and cos.shape == sin.shape and cos.shape[-1] == n_rot // 2, "rotation tables must be float32 [P, n_rot/2]")
+        _need(ctx.max_kv_len <= cos.shape[0],
+              f"rotation tables hold {cos.shape[0]} positions, the step reaches position {ctx.max_kv_len}")
+    page = pages.shape[2]
+    _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (1, page, C + R) and pages.dtype == cq_out.dtype,
+          "latent_prep: pages [n_pages, 1, page, C + R] of the activation dtype")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+          and ctx.max_kv_len <= table.shape[1] * page, "latent_prep: the block table does not cover the step")
+    _need(cq_out.is_contiguous() and cq_out.shape[-1] == Q and cq_out.numel() >= T * Q, "latent_prep: cq_out [T, Q]")
+    _i32(ctx.tok_pos, T, "tok_pos")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _check(_lib("latent_attention").ab_latent_prep(
+        _p(x), x.shape[-1], Q, C, R, _p(q_norm_weight), _p(c_norm_weight), ctypes.c_float(eps), _p(cos), _p(sin), n_rot,
+        _p(ctx.tok_pos), _p(ctx.tok_seq), _p(table), table.shape[1], page, _p(pages), _p(cq_out), _dt(cq_out), T,
+        1 if write_cache else 0, _stream()), "latent_prep")
+    return cq_out
+
+
+def heads_matmul(a, a_head_stride, w, out, out_head_stride, n_tokens, tail=0, rot=None, ctx=None):
+    """out[t, h, :N] = w[h] @ a[t, h, :K] for w [H, N, K]; a [T, H * a_head_stride], out [T, H * out_head_stride].
+    `tail` dims behind the K read ones are copied behind the N written ones, the first n_rot of them rotated by
+    position in pairs (2i, 2i+1) (`rot` = (cos, sin, n_rot, 0), positions and padding rows from `ctx`)."""
+    cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
+    _cuda(a, w, out, cos, sin)
+    H, N, K = w.shape
+    _need(w.is_contiguous() and a.is_contiguous() and out.is_contiguous(), "heads_matmul takes contiguous tensors")
+    _need(a.shape[-1] == H * a_head_stride and K + tail <= a_head_stride and a.numel() >= n_tokens * a.shape[-1],
+          "heads_matmul: a [T, H * a_head_stride]")
+    _need(out.shape[-1] == H * out_head_stride and N + tail <= out_head_stride
+          and out.numel() >= n_tokens * out.shape[-1], "heads_matmul: out [T, H * out_head_stride]")
+    _need(pairing == 0 and n_rot <= tail, "heads_matmul rotates pairs (2i, 2i+1) of the tail only")
+    tok_pos = tok_seq = None
+    if ctx is not None:
+        tok_pos, tok_seq = ctx.tok_pos, ctx.tok_seq
+        _i32(tok_pos, n_tokens, "tok_pos")
+        _i32(tok_seq, n_tokens, "tok_seq")
+    _need(n_rot == 0 or (tok_pos is not None and cos is not None and cos.dtype == torch.float32
+                         and cos.shape[-1] == n_rot // 2 and ctx.max_kv_len <= cos.shape[0]),
+          "heads_matmul: a rotated tail needs positions and tables that cover them")
+    _check(_lib("latent_attention").ab_heads_matmul(
+        _p(a), _dt(a), a.shape[-1], a_head_stride, _p(w), _dt(w), _p(out), _dt(out), out.shape[-1], out_head_stride,
+        n_tokens, H, N, K, tail, _p(cos), _p(sin), n_rot, _p(tok_pos), _p(tok_seq), _stream()), "heads_matmul")
+    return out
+
+
+def latent_attention(q, out, cache, ctx, H, C, R, scale, sink=None):
+    """Attention of every token over its sequence's cached latent rows [c | r] (see csrc/latent_attention.cu).
+    q float32 [T, H*(C+R)] (keys' up-projection folded in), out float32 [T, H*C], sink float32 [H] or None."""
+    pages, table = cache.k, cache.block_table
+    _cuda(q, out, pages, table, sink)
+    T = ctx.n_tokens
+    _need(q.dtype == torch.float32 and out.dtype == torch.float32 and q.is_contiguous() and out.is_contiguous()
+          and q.shape[-1] == H * (C + R) and out.shape[-1] == H * C and q.numel() >= T * H * (C + R)
+          and out.numel() >= T * H * C, "latent_attention: q float32 [T, H*(C+R)], out float32 [T, H*C]")
+    page = pages.shape[2]
+    _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (1, page, C + R),
+          "latent_attention: pages [n_pages, 1, page, C + R]")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+          and ctx.max_kv_len <= table.shape[1] * page, "latent_attention: the block table does not cover the step")
+    if sink is not None:
+        _need(sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous(), "sink must be float32 [H]")
+    _need(C + R <= 1024, f"latent_attention: rows of {C + R} dims are outside 1..1024")
+    _i32(ctx.tok_pos, T, "tok_pos")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _check(_lib("latent_attention").ab_latent_attention_simt(
+        _p(q), _p(out), _p(pages), _dt(pages), _p(table), table.shape[1], _p(ctx.tok_pos), _p(ctx.tok_seq), _p(sink),
+        T, H, C, R, page, ctypes.c_float(scale), _stream()), "latent_attention")
+    return out
+
+
+MOE_ACTIVATIONS = {"gelu": 0, "silu": 1}
+
+
+def moe_route(h, router, n_tokens, groups, keep, top, scale):
+    """(experts int32 [T, top], weights float32 [T, top]) of every token: softmax over all experts, the `keep`
+    best of `groups` groups of neighbours, the `top` best experts of those, weights renormalised times `scale`."""
+    _cuda(h, router)
+    E, width = router.shape
+    _need(router.dtype == torch.float32 and router.is_contiguous(), "the router's matrix must be float32")
+    _need(h.is_contiguous() and h.shape[-1] == width and h.numel() >= n_tokens * width, "moe_route: h [T, width]")
+    _need(E <= 1024 and groups > 0 and E % groups == 0 and 0 < keep <= groups and 0 < top <= keep * (E // groups),
+          f"moe_route: {E} experts in {groups} groups, {keep} kept, {top} chosen cannot be routed")
+    idx = torch.empty((max(n_tokens, 1), top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((max(n_tokens, 1), top), dtype=torch.float32, device=h.device)
+    _check(_lib("moe").ab_moe_route(_p(h), _dt(h), width, _p(router), n_tokens, width, E, groups, keep, top,
+                                    ctypes.c_float(scale), _p(idx), _p(wts), _stream()), "moe_route")
+    return idx, wts
+
+
+def moe_experts(h, w_up, w_down, idx, wts, out, n_tokens, activation="gelu"):
+    """out[t] = sum_j wts[t, j] * w_down[idx[t, j]] @ act(w_up[idx[t, j]] @ h[t]); w_up [E, ff, width],
+    w_down [E, width, ff], all of h's dtype."""
+    _cuda(h, w_up, w_down, idx, wts, out)
+    E, ff, width = w_up.shape
+    top = idx.shape[-1]
+    _need(tuple(w_down.shape) == (E, width, ff) and w_up.is_contiguous() and w_down.is_contiguous()
+          and w_up.dtype == h.dtype and w_down.dtype == h.dtype, "moe_experts: w_up [E, ff, width], w_down [E, width, ff]")
+    _need(h.is_contiguous() and h.shape[-1] == width and out.is_contiguous() and out.shape[-1] == width
+          and out.dtype == h.dtype and out.numel() >= n_tokens * width, "moe_experts: h, out [T, width] of one dtype")
+    _i32(idx, n_tokens * top, "experts")
+    _need(wts.dtype == torch.float32 and wts.is_contiguous() and wts.numel() >= n_tokens * top, "weights float32 [T, top]")
+    act = torch.empty((max(n_tokens, 1) * top, ff), dtype=h.dtype, device=h.device)
+    _check(_lib("moe").ab_moe_pairs(_p(h), _dt(h), width, _p(w_up), _p(w_down), _p(idx), _p(wts), _p(act), _p(out),
+                                    n_tokens, top, width, ff, E, MOE_ACTIVATIONS[activation], _stream()), "moe_experts")
+    return out

@@ -1,12 +1,15 @@
 from .attention import Attention
 from .base import (Block, BuildOptions, FeedForward, KVSpec, Mixer, Norm, Part, PositionEncoding, StateSpec)
-from .block import HiddenStream, PreNormBlock
+from .block import HiddenStream, ParallelBlock, PreNormBlock
 from .embedding import TokenEmbedding, VocabHead
+from .experts import RoutedExperts
 from .feedforward import SwiGLU
+from .latent_attention import LatentAttention
 from .linear import Linear
+from .mlstm import MatrixMemory
 from .norm import RMSNorm
 from .position import RotaryEncoding, scaled_inv_freq
 
 __all__ = ["Attention", "Block", "BuildOptions", "FeedForward", "KVSpec", "Mixer", "Norm", "Part", "PositionEncoding",
-           "StateSpec", "HiddenStream", "PreNormBlock", "TokenEmbedding", "VocabHead", "SwiGLU", "Linear",
+           "StateSpec", "HiddenStream", "PreNormBlock", "ParallelBlock", "RoutedExperts", "LatentAttention", "MatrixMemory", "TokenEmbedding", "VocabHead", "SwiGLU", "Linear",
            "RMSNorm", "RotaryEncoding", "scaled_inv_freq"]

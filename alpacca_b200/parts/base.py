@@ -46,10 +46,12 @@ class BuildOptions:
 @dataclass(frozen=True)
 class KVSpec:
     """The mixer keeps keys and values of `n_kv_heads` x `head_dim` per token;
-    `window` = how many of the latest keys it reads (None: all)."""
+    `window` = how many of the latest keys it reads (None: all).  `values` off: one row per token and
+    head only (a mixer whose values are part of its key rows, such as a cached latent)."""
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    values: bool = True
 
 
 @dataclass(frozen=True)

@@ -14,6 +14,7 @@ from dataclasses import dataclass
 
 import torch
 
+from .. import ops
 from .base import Block, FeedForward, Mixer, Norm, OwedNorm
 
 
@@ -47,6 +48,24 @@ class PreNormBlock(Block):
         _sublayer(stream, after_mixer, self.mixer, h, ctx, cache, write_cache)
         h = _normed(self.norm2, stream)
         _sublayer(stream, next_norm, self.ffn, h, ctx)
+
+
+class ParallelBlock(Block):
+    """One norm, both sub-layers read its output: h = Norm(x); x += Mixer(h) + FeedForward(h).
+    The stream is float32: the mixer's output is added to it at once and the feed-forward's waits for the
+    next norm's kernel, so neither the sum of the two nor the stream is rounded to the activation dtype."""
+
+    def __init__(self, norm: Norm, mixer: Mixer, ffn: FeedForward | None):
+        self.norm1, self.mixer, self.ffn = norm, mixer, ffn
+
+    def forward(self, stream: HiddenStream, ctx, cache, write_cache: bool = True) -> None:
+        stream.next_norm = None
+        h = _normed(self.norm1, stream)
+        stream.delta = self.mixer.forward(h, ctx, cache, write_cache)
+        if self.ffn is None:
+            return
+        ops.residual_add(stream.residual, stream.delta, n_rows=ctx.n_tokens)
+        stream.delta = self.ffn.forward(h, ctx)
 
 
 def _accepts(part, n_rows: int) -> bool:

@@ -13,12 +13,13 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
-    def __init__(self, opts: BuildOptions, vocab: int, width: int, name: str):
+    def __init__(self, opts: BuildOptions, vocab: int, width: int, name: str, weight_suffix: str = ".weight"):
         self.opts, self.vocab, self.width, self.name = opts, int(vocab), int(width), name
+        self.weight_suffix = weight_suffix
         self.weight = None
 
     def own_param_specs(self):
-        return [ParamSpec(f"{self.name}.weight", (self.vocab, self.width), "matrix", "normal")]
+        return [ParamSpec(f"{self.name}{self.weight_suffix}", (self.vocab, self.width), "matrix", "normal")]
 
     def load_own(self, fetch):
         self.weight = fetch(self.own_param_specs()[0])
@@ -30,17 +31,17 @@ class TokenEmbedding(Part):
 
 class VocabHead(Part):
     def __init__(self, opts: BuildOptions, vocab: int, width: int, name: str,
-                 tied_to: TokenEmbedding | None = None):
+                 tied_to: TokenEmbedding | None = None, weight_suffix: str = ".weight"):
         self.opts, self.vocab, self.width, self.name = opts, int(vocab), int(width), name
-        self.tied_to = tied_to
-        self.proj = Linear(opts, width, [(name, vocab)], out_dtype=torch.float32)
+        self.tied_to, self.weight_suffix = tied_to, weight_suffix
+        self.proj = Linear(opts, width, [(name, vocab)], out_dtype=torch.float32, weight_suffix=weight_suffix)
 
     def children(self):
         return [] if self.tied_to is not None else [self.proj]
 
     def own_param_specs(self):
         if self.tied_to is not None:   # declared so that a stray stored head is reported, not ignored
-            return [ParamSpec(f"{self.name}.weight", (self.vocab, self.width), "matrix", absent=True)]
+            return [ParamSpec(f"{self.name}{self.weight_suffix}", (self.vocab, self.width), "matrix", absent=True)]
         return []
 
     def load_own(self, fetch):

@@ -12,15 +12,17 @@ from .linear import Linear
 
 class SwiGLU(FeedForward):
     def __init__(self, opts: BuildOptions, width: int, inner: int, prefix: str, bias: bool = False,
-                 names=("gate_proj", "up_proj", "down_proj")):
+                 names=("gate_proj", "up_proj", "down_proj"), weight_suffix: str = ".weight",
+                 out_dtype=None):
         if inner % 8:
             raise ValueError(f"feed-forward width {inner} must be a multiple of 8 "
                              "(gate and up rows are interleaved in groups of 8)")
         self.opts, self.width, self.inner = opts, int(width), int(inner)
         g, u, d = names
         self.gate_up = Linear(opts, width, [(f"{prefix}.{g}", inner), (f"{prefix}.{u}", inner)], bias=bias,
-                              interleave8=True)
-        self.down = Linear(opts, inner, [(f"{prefix}.{d}", width)], bias=bias)
+                              interleave8=True, weight_suffix=weight_suffix)
+        self.down = Linear(opts, inner, [(f"{prefix}.{d}", width)], bias=bias, weight_suffix=weight_suffix,
+                           out_dtype=out_dtype)
 
     adds_to_residual = True
 

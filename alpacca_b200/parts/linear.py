@@ -17,9 +17,10 @@ from .base import BuildOptions, OwedNorm, Part
 
 class Linear(Part):
     def __init__(self, opts: BuildOptions, in_features: int, sources, bias: bool = False,
-                 interleave8: bool = False, out_dtype: torch.dtype | None = None):
+                 interleave8: bool = False, out_dtype: torch.dtype | None = None, weight_suffix: str = ".weight"):
         """`sources`: list of (checkpoint prefix, rows); tensors `<prefix>.weight`
-        [rows, in] (and `<prefix>.bias` [rows]) are stacked in that order.
+        [rows, in] (and `<prefix>.bias` [rows]) are stacked in that order
+        (`weight_suffix` "" for checkpoints that name a matrix by its prefix alone).
         `interleave8`: two sources of equal size are interleaved in groups of 8
         rows (8 of the first, 8 of the second, ...), the layout `ops.swiglu` reads.
         `out_dtype` float32 gives float32 results from bfloat16 inputs (logits)."""
@@ -30,6 +31,7 @@ class Linear(Part):
         self.has_bias = bool(bias)
         self.interleave8 = bool(interleave8)
         self.out_dtype = out_dtype or opts.dtype
+        self.weight_suffix = weight_suffix
         if interleave8:
             if len(self.sources) != 2 or self.sources[0][1] != self.sources[1][1] or self.sources[0][1] % 8:
                 raise ValueError("interleave8 needs two sources of equal size, a multiple of 8 rows "
@@ -38,7 +40,7 @@ class Linear(Part):
         self.bias = None
 
     def own_param_specs(self):
-        specs = [ParamSpec(f"{p}.weight", (r, self.in_features), "matrix", "normal") for p, r in self.sources]
+        specs = [ParamSpec(f"{p}{self.weight_suffix}", (r, self.in_features), "matrix", "normal") for p, r in self.sources]
         if self.has_bias:
             specs += [ParamSpec(f"{p}.bias", (r,), "vector", "normal") for p, r in self.sources]
         return specs
@@ -53,7 +55,7 @@ class Linear(Part):
         return torch.cat(tensors, dim=0).contiguous()
 
     def load_own(self, fetch):
-        self.weight = self._stack([fetch(ParamSpec(f"{p}.weight", (r, self.in_features), "matrix"))
+        self.weight = self._stack([fetch(ParamSpec(f"{p}{self.weight_suffix}", (r, self.in_features), "matrix"))
                                    for p, r in self.sources])
         if self.has_bias:
             self.bias = self._stack([fetch(ParamSpec(f"{p}.bias", (r,), "vector")) for p, r in self.sources])

@@ -1,7 +1,9 @@
-"""RMSNorm with a plain weight, fused with the residual add that precedes it.
+"""RMSNorm, fused with the residual add that precedes it.
 
 inv = 1/sqrt(mean(x^2) + eps); y = (x * inv) * w  (alpacca/tensor.py:163-173);
-the weight multiplies as it is (not 1 + w), eps is inside the root.
+eps is inside the root.  The weight multiplies as it is, or, for checkpoints
+that store it around zero (`unit_offset`), as 1 + w: the sum is formed once,
+in float32, when the weight is loaded.
 """
 from __future__ import annotations
 
@@ -13,15 +15,20 @@ from .base import BuildOptions, Norm
 
 
 class RMSNorm(Norm):
-    def __init__(self, opts: BuildOptions, width: int, eps: float, name: str):
+    def __init__(self, opts: BuildOptions, width: int, eps: float, name: str, weight_suffix: str = ".weight",
+                 unit_offset: bool = False):
         self.opts, self.width, self.eps, self.name = opts, int(width), float(eps), name
+        self.weight_suffix, self.unit_offset = weight_suffix, bool(unit_offset)
         self.weight = None
 
     def own_param_specs(self):
-        return [ParamSpec(f"{self.name}.weight", (self.width,), "vector", "one_plus_normal")]
+        return [ParamSpec(f"{self.name}{self.weight_suffix}", (self.width,), "vector",
+                          "normal" if self.unit_offset else "one_plus_normal")]
 
     def load_own(self, fetch):
         self.weight = fetch(self.own_param_specs()[0])
+        if self.unit_offset:
+            self.weight = (self.weight + 1.0).contiguous()
 
     def deferred(self):
         if self.opts.dtype != torch.bfloat16 or self.weight is None:
