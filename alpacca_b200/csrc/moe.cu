@@ -52,7 +52,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int ld, const float* _
       gs[g] = v;
     }
     __syncwarp();
-    for (int round = 0; round < keep; ++round) {
+    for (int pick = 0; pick < keep; ++pick) {
       float best = -0.5f;
       int bg = 0x7fffffff;
       for (int g = lane; g < groups; g += 32)
@@ -71,7 +71,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int ld, const float* _
     __syncwarp();
   }
   float chosen_sum = 0.f;
-  for (int round = 0; round < top; ++round) {
+  for (int pick = 0; pick < top; ++pick) {
     float best = -0.5f;
     int be = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
@@ -87,8 +87,8 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int ld, const float* _
     if (be == 0x7fffffff) { be = 0; best = 0.f; }      // nothing left to choose (or the row holds no numbers)
     chosen_sum += best;
     if (lane == 0) {
-      idx[(size_t)t * top + round] = be;
-      wts[(size_t)t * top + round] = best;
+      idx[(size_t)t * top + pick] = be;
+      wts[(size_t)t * top + pick] = best;
       s[be] = -1.f;                                    // taken
     }
     __syncwarp();

@@ -1,7 +1,7 @@
 """The Lefatar decoder, put together from the parts.
 
 Layers as config.json lists them, each a parallel block: h = norm1(x); x += mixer(h) + ff(h), with a norm
-whose weight is stored around zero.  A layer's mixer is the matrix memory (`mlstm`) or causal attention over
+that multiplies by 1 + w for its stored w.  A layer's mixer is the matrix memory (`mlstm`) or causal attention over
 a cached latent with a sink (`latent_attention`); its feed-forward is the gated dense one (SiLU), routed
 experts (exact GELU, grouped router) or none.  A final norm of the same kind, then the head.
 

@@ -1,9 +1,9 @@
 """RMSNorm, fused with the residual add that precedes it.
 
 inv = 1/sqrt(mean(x^2) + eps); y = (x * inv) * w  (alpacca/tensor.py:163-173);
-eps is inside the root.  The weight multiplies as it is, or, for checkpoints
-that store it around zero (`unit_offset`), as 1 + w: the sum is formed once,
-in float32, when the weight is loaded.
+eps is inside the root.  The weight multiplies as it is, or, with `unit_offset`
+(checkpoints that keep w = weight - 1), as 1 + w: the sum is formed once, in
+float32, when the weight is loaded.
 """
 from __future__ import annotations
 

@@ -19,7 +19,7 @@ def rms_unit(x, eps):
 
 
 def norm_offset(x, w, eps):
-    """The layer norm and the final norm: the weight is stored around zero."""
+    """The layer norm and the final norm multiply by 1 + w."""
     return rms_unit(x, eps) * (1.0 + w)
 
 
