@@ -162,6 +162,12 @@ __device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int 
   }
 }
 
+// A sink: a learned logit per head whose exp joins the softmax's denominator and which has no value.  `m` is
+// the row's running maximum in the kernels' units (scaled scores times log2 e), `l` its sum of exp2(score - m).
+__device__ __forceinline__ float sum_with_sink(float l, float m, const float* __restrict__ sink, int h) {
+  return sink == nullptr ? l : l + exp2f(sink[h] * LOG2E - m);
+}
+
 // ---------------------------------------------------------------------------
 // prefill
 // ---------------------------------------------------------------------------
@@ -172,7 +178,7 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_pos,
                          const int* __restrict__ cu_q, const int* __restrict__ tile_seq,
                          const int* __restrict__ tile_q0, int H, int K, int D, float scale_log2, int window,
-                         int tokens_per_tile) {
+                         int tokens_per_tile, const float* __restrict__ sink) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch = D + 8;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);            // [64][pitch]
@@ -246,6 +252,8 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (r0 < n_rows) l0 = sum_with_sink(l0, st.m[0], sink, kh * G + r0 % G);
+  if (r1 < n_rows) l1 = sum_with_sink(l1, st.m[1], sink, kh * G + r1 % G);
   const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
 #pragma unroll
   for (int dt = 0; dt < DMAX / 8; ++dt) {
@@ -400,7 +408,7 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_seq,
                         const int* __restrict__ kv_len, int H, int K, int D, float scale_log2, int window,
                         int pages_per_cta, int n_chunks, int cluster_merge, bf16* k_out, bf16* v_out, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                        int n_rot, int pairing, int fuse) {
+                        int n_rot, int pairing, int fuse, const float* __restrict__ sink) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch = D + 8;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                 // [8][pitch] q, [2][pitch] this step's k, v
@@ -585,6 +593,7 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
       cta_o[r * D + d] = o;
       if (d == 0) { cta_ml[r * 2] = m; cta_ml[r * 2 + 1] = l; }
     } else if (single) {
+      l = sum_with_sink(l, m, sink, h);
       out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     } else {
       const size_t p = ((size_t)tok * H + h) * n_chunks + chunk;
@@ -611,6 +620,7 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
           l += ml[r * 2 + 1] * f;
           o += cluster.map_shared_rank(cta_o, c)[r * D + d] * f;
         }
+        l = sum_with_sink(l, m, sink, kh * G + rt * 8 + r);
         out[((size_t)tok * H + kh * G + rt * 8 + r) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
       }
     }
@@ -649,6 +659,7 @@ attention_decode_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __rest
       l += __ldcg(part_ml + (base + c) * 2 + 1) * f;
       o += __ldcg(part_o + (base + c) * D + d) * f;
     }
+    l = sum_with_sink(l, m, sink, h);
     out[((size_t)tok * H + h) * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
   }
 }
@@ -672,11 +683,12 @@ AB_API int ab_attention_decode_round_keys(int D, int small) {
 }
 AB_API int ab_attention_decode_round_pages(int D) { return ab_attention_decode_round_keys(D, 0) / PAGE; }
 
-AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
-                                     const void* v_pages, const int* block_table, int table_width,
-                                     const int* tok_pos, const int* cu_q, const int* tile_seq, const int* tile_q0,
-                                     int n_tiles, int tokens_per_tile, int H, int K, int D, float scale, int window,
-                                     cudaStream_t stream) {
+// `sink`: float [H] or null (see sum_with_sink).
+AB_API int ab_attention_prefill_sink_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
+                                          const void* v_pages, const int* block_table, int table_width,
+                                          const int* tok_pos, const int* cu_q, const int* tile_seq, const int* tile_q0,
+                                          int n_tiles, int tokens_per_tile, int H, int K, int D, float scale, int window,
+                                          const float* sink, cudaStream_t stream) {
   if (n_tiles <= 0) return AB_OK;
   if (D <= 0 || D > 256 || (D % 16) || H % K || K > 65535) return AB_BAD_ARG;
   const int G = H / K;
@@ -693,7 +705,7 @@ AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, c
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
     ab_launch(attention_prefill_kernel<DM>, grid, dim3(128), smem, stream,                                         \
         (const bf16*)qkv, q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages, block_table,           \
-        table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, D, sl, window, tokens_per_tile);                      \
+        table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, D, sl, window, tokens_per_tile, sink);                \
   }
   switch (dmax_of(D)) {
     case 64: AB_GO(64); break;
@@ -702,6 +714,16 @@ AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, c
   }
 #undef AB_GO
   return ab_launch_status();
+}
+
+AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
+                                     const void* v_pages, const int* block_table, int table_width,
+                                     const int* tok_pos, const int* cu_q, const int* tile_seq, const int* tile_q0,
+                                     int n_tiles, int tokens_per_tile, int H, int K, int D, float scale, int window,
+                                     cudaStream_t stream) {
+  return ab_attention_prefill_sink_bf16(qkv, q_stride, out, k_pages, v_pages, block_table, table_width, tok_pos, cu_q,
+                                        tile_seq, tile_q0, n_tiles, tokens_per_tile, H, K, D, scale, window, nullptr,
+                                        stream);
 }
 
 // Launch with programmatic dependent launch and, for `cluster_z` > 1, clusters of that many CTAs along z.
@@ -746,6 +768,13 @@ AB_API int ab_attention_decode_rope_bf16(const void* qkv, int q_stride, void* ou
 // part_o float [n_tokens * H * n_chunks, D], part_ml float [n_tokens * H * n_chunks, 2], arrivals int
 // [n_tokens * K * ceil(G / 8)], which must be zero before the first launch and is left zero by every
 // launch.
+AB_API int ab_attention_decode_sink_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
+                                         int* arrivals, void* k_pages, void* v_pages, const int* block_table,
+                                         int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
+                                         int K, int D, float scale, int window, int pages_per_cta, int n_chunks,
+                                         int small, const float* cos_t, const float* sin_t, int n_rot, int pairing,
+                                         int fuse, const float* sink, cudaStream_t stream);
+
 AB_API int ab_attention_decode_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
                                     int* arrivals, const void* k_pages, const void* v_pages, const int* block_table,
                                     int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
@@ -766,6 +795,18 @@ AB_API int ab_attention_decode_rope_bf16(const void* qkv, int q_stride, void* ou
                                          int K, int D, float scale, int window, int pages_per_cta, int n_chunks,
                                          int small, const float* cos_t, const float* sin_t, int n_rot, int pairing,
                                          int fuse, cudaStream_t stream) {
+  return ab_attention_decode_sink_bf16(qkv, q_stride, out, part_o, part_ml, arrivals, k_pages, v_pages, block_table,
+                                       table_width, tok_seq, kv_len, n_tokens, H, K, D, scale, window, pages_per_cta,
+                                       n_chunks, small, cos_t, sin_t, n_rot, pairing, fuse, nullptr, stream);
+}
+
+// The same with a sink per head in the softmax's denominator (`sink`: float [H] or null).
+AB_API int ab_attention_decode_sink_bf16(const void* qkv, int q_stride, void* out, float* part_o, float* part_ml,
+                                         int* arrivals, void* k_pages, void* v_pages, const int* block_table,
+                                         int table_width, const int* tok_seq, const int* kv_len, int n_tokens, int H,
+                                         int K, int D, float scale, int window, int pages_per_cta, int n_chunks,
+                                         int small, const float* cos_t, const float* sin_t, int n_rot, int pairing,
+                                         int fuse, const float* sink, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (D <= 0 || D > 256 || (D % 16) || H % K || n_chunks < 1 || n_chunks > 65535 || pages_per_cta < 1)
     return AB_BAD_ARG;
@@ -792,7 +833,7 @@ AB_API int ab_attention_decode_rope_bf16(const void* qkv, int q_stride, void* ou
         cluster_merge ? (unsigned)n_chunks : 1u,                                                                    \
         (const bf16*)qkv, q_stride, (bf16*)out, part_o, part_ml, arrivals, (const bf16*)k_pages,                    \
         (const bf16*)v_pages, block_table, table_width, tok_seq, kv_len, H, K, D, sl, window, pages_per_cta,        \
-        n_chunks, cluster_merge, (bf16*)k_pages, (bf16*)v_pages, cos_t, sin_t, n_rot, pairing, fuse);               \
+        n_chunks, cluster_merge, (bf16*)k_pages, (bf16*)v_pages, cos_t, sin_t, n_rot, pairing, fuse, sink);         \
   }
   if (n_chunks > AB_DECODE_MAX_CLUSTER && (!part_o || !part_ml || !arrivals)) return AB_BAD_ARG;
   switch (dmax_of(D)) {

@@ -75,12 +75,13 @@ AB_API int ab_latent_prep(const float* x, int ld, int Q, int C, int R, const flo
 
 // ---------------------------------------------------------------------------------------------
 // a: [T, H, a_hs] (row stride lda), w: [H, N, K], out: [T, H, o_hs] (row stride ldo).  Warp per (t, h, n).
-// tail > 0: out[t, h, N + j] = a[t, h, K + j] for j < tail, its first n_rot dims rotated in pairs (2i, 2i+1).
+// tail > 0: out[t, h, tail_at + j] = a[t, h, K + j] for j < tail, its first n_rot dims rotated in pairs (2i, 2i+1).
 template <typename TA, typename TW, typename TO>
 __global__ void heads_matmul_kernel(const TA* __restrict__ a, int lda, int a_hs, const TW* __restrict__ w,
                                     TO* __restrict__ out, int ldo, int o_hs, int n_tokens, int H, int N, int K,
-                                    int tail, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                    int n_rot, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq) {
+                                    int tail, int tail_at, const float* __restrict__ cos_t,
+                                    const float* __restrict__ sin_t, int n_rot, const int* __restrict__ tok_pos,
+                                    const int* __restrict__ tok_seq) {
   const int lane = threadIdx.x & 31;
   const int per = N + tail;
   const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -107,38 +108,42 @@ __global__ void heads_matmul_kernel(const TA* __restrict__ a, int lda, int a_hs,
     const float cs = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
     v = (j & 1) ? v * cs + to_f32(av[K + j - 1]) * sn : v * cs - to_f32(av[K + j + 1]) * sn;
   }
-  o[N + j] = from_f32<TO>(v);
+  o[tail_at + j] = from_f32<TO>(v);
 }
 
 template <typename TA, typename TW, typename TO>
 static int heads_go(const void* a, int lda, int a_hs, const void* w, void* out, int ldo, int o_hs, int n_tokens, int H,
-                    int N, int K, int tail, const float* cos_t, const float* sin_t, int n_rot, const int* tok_pos,
-                    const int* tok_seq, cudaStream_t stream) {
+                    int N, int K, int tail, int tail_at, const float* cos_t, const float* sin_t, int n_rot,
+                    const int* tok_pos, const int* tok_seq, cudaStream_t stream) {
   const long long warps = (long long)n_tokens * H * (N + tail);
   const int wpb = 8;
   const long long blocks = (warps + wpb - 1) / wpb;
   if (blocks > 0x7fffffffLL) return AB_BAD_ARG;
   heads_matmul_kernel<TA, TW, TO><<<(unsigned)blocks, wpb * 32, 0, stream>>>(
-      (const TA*)a, lda, a_hs, (const TW*)w, (TO*)out, ldo, o_hs, n_tokens, H, N, K, tail, cos_t, sin_t, n_rot, tok_pos,
-      tok_seq);
+      (const TA*)a, lda, a_hs, (const TW*)w, (TO*)out, ldo, o_hs, n_tokens, H, N, K, tail, tail_at, cos_t, sin_t, n_rot,
+      tok_pos, tok_seq);
   return ab_launch_status();
 }
 
 // dtypes: a, w, out each AB_F32 or AB_BF16; supported: (f32,f32,f32), (bf16,bf16,f32), (bf16,bf16,bf16), (f32,bf16,bf16),
 // (f32,bf16,f32)
 AB_API int ab_heads_matmul(const void* a, int a_dt, int lda, int a_hs, const void* w, int w_dt, void* out, int o_dt,
-                           int ldo, int o_hs, int n_tokens, int H, int N, int K, int tail, const float* cos_t,
-                           const float* sin_t, int n_rot, const int* tok_pos, const int* tok_seq, cudaStream_t stream) {
+                           int ldo, int o_hs, int n_tokens, int H, int N, int K, int tail, int tail_at,
+                           const float* cos_t, const float* sin_t, int n_rot, const int* tok_pos, const int* tok_seq,
+                           cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
-  if (H <= 0 || N <= 0 || K <= 0 || tail < 0 || n_rot > tail || (n_rot & 1)) return AB_BAD_ARG;
+  if (H <= 0 || N < 0 || N + tail <= 0 || K <= 0 || tail < 0 || n_rot > tail || (n_rot & 1) || tail_at < N ||
+      tail_at + tail > o_hs)
+    return AB_BAD_ARG;
 #define AB_HM(TA, TW, TO)                                                                                        \
-  return heads_go<TA, TW, TO>(a, lda, a_hs, w, out, ldo, o_hs, n_tokens, H, N, K, tail, cos_t, sin_t, n_rot, tok_pos, \
-                              tok_seq, stream)
+  return heads_go<TA, TW, TO>(a, lda, a_hs, w, out, ldo, o_hs, n_tokens, H, N, K, tail, tail_at, cos_t, sin_t, n_rot, \
+                              tok_pos, tok_seq, stream)
   if (a_dt == AB_F32 && w_dt == AB_F32 && o_dt == AB_F32) AB_HM(float, float, float);
   if (a_dt == AB_BF16 && w_dt == AB_BF16 && o_dt == AB_F32) AB_HM(bf16, bf16, float);
   if (a_dt == AB_BF16 && w_dt == AB_BF16 && o_dt == AB_BF16) AB_HM(bf16, bf16, bf16);
   if (a_dt == AB_F32 && w_dt == AB_BF16 && o_dt == AB_BF16) AB_HM(float, bf16, bf16);
   if (a_dt == AB_F32 && w_dt == AB_BF16 && o_dt == AB_F32) AB_HM(float, bf16, float);
+  if (a_dt == AB_BF16 && w_dt == AB_F32 && o_dt == AB_BF16) AB_HM(bf16, float, bf16);
 #undef AB_HM
   return AB_BAD_ARG;
 }

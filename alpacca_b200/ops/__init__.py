@@ -1001,17 +1001,22 @@ def latent_prep(x, Q, C, R, q_norm_weight, c_norm_weight, eps, rot, ctx, cache, 
     return cq_out
 
 
-def heads_matmul(a, a_head_stride, w, out, out_head_stride, n_tokens, tail=0, rot=None, ctx=None):
+def heads_matmul(a, a_head_stride, w, out, out_head_stride, n_tokens, tail=0, rot=None, ctx=None, tail_at=None):
     """out[t, h, :N] = w[h] @ a[t, h, :K] for w [H, N, K]; a [T, H * a_head_stride], out [T, H * out_head_stride].
     `tail` dims behind the K read ones are copied behind the N written ones, the first n_rot of them rotated by
     position in pairs (2i, 2i+1) (`rot` = (cos, sin, n_rot, 0), positions and padding rows from `ctx`)."""
     cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
     _cuda(a, w, out, cos, sin)
-    H, N, K = w.shape
+    if w is None:                  # the tail alone, written `tail_at` dims into each head of `out`
+        H, N, K = a.shape[-1] // a_head_stride, 0, a_head_stride - tail
+        w = a
+    else:
+        H, N, K = w.shape
+    tail_at = N if tail_at is None else int(tail_at)
     _need(w.is_contiguous() and a.is_contiguous() and out.is_contiguous(), "heads_matmul takes contiguous tensors")
     _need(a.shape[-1] == H * a_head_stride and K + tail <= a_head_stride and a.numel() >= n_tokens * a.shape[-1],
           "heads_matmul: a [T, H * a_head_stride]")
-    _need(out.shape[-1] == H * out_head_stride and N + tail <= out_head_stride
+    _need(out.shape[-1] == H * out_head_stride and N <= tail_at and tail_at + tail <= out_head_stride
           and out.numel() >= n_tokens * out.shape[-1], "heads_matmul: out [T, H * out_head_stride]")
     _need(pairing == 0 and n_rot <= tail, "heads_matmul rotates pairs (2i, 2i+1) of the tail only")
     tok_pos = tok_seq = None
@@ -1024,7 +1029,66 @@ def heads_matmul(a, a_head_stride, w, out, out_head_stride, n_tokens, tail=0, ro
           "heads_matmul: a rotated tail needs positions and tables that cover them")
     _check(_lib("latent_attention").ab_heads_matmul(
         _p(a), _dt(a), a.shape[-1], a_head_stride, _p(w), _dt(w), _p(out), _dt(out), out.shape[-1], out_head_stride,
-        n_tokens, H, N, K, tail, _p(cos), _p(sin), n_rot, _p(tok_pos), _p(tok_seq), _stream()), "heads_matmul")
+        n_tokens, H, N, K, tail, tail_at, _p(cos), _p(sin), n_rot, _p(tok_pos), _p(tok_seq), _stream()), "heads_matmul")
+    return out
+
+
+def latent_attention_mma_supports(H, C, R, dtype) -> bool:
+    """Whether `latent_attention_mma` takes these sizes: bfloat16, rows of C + R dims in steps of 16 up to 256,
+    up to 64 heads (all heads of a token share its keys: they are the rows of one tile)."""
+    return dtype == torch.bfloat16 and (C + R) % 16 == 0 and 0 < C + R <= 256 and 0 < H <= 64
+
+
+def latent_attention_mma(q, out, cache, ctx, H, C, R, scale, sink=None):
+    """The same attention on the tensor-core kernels of csrc/attention_mma.cu: the cached rows [c | r] are one
+    key/value head of C + R dims that all H query heads share, the values are the rows themselves (the first C
+    dims of a head's output are its weighted sum of c), and the sink joins the denominator in the kernels' last
+    step.  q, out bfloat16 [T, H*(C+R)]."""
+    pages, table = cache.k, cache.block_table
+    _cuda(q, out, pages, table, sink)
+    T, D = ctx.n_tokens, C + R
+    _need(latent_attention_mma_supports(H, C, R, q.dtype), f"latent_attention_mma: {H} heads of {D} dims not supported")
+    _need(out.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous()
+          and q.shape[-1] == H * D and out.shape[-1] == H * D and q.numel() >= T * H * D and out.numel() >= T * H * D,
+          "latent_attention_mma: q, out bfloat16 [T, H*(C+R)]")
+    _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (1, 64, D), "latent_attention_mma: pages [n_pages, 1, 64, C+R]")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+          and ctx.max_kv_len <= table.shape[1] * 64, "latent_attention_mma: the block table does not cover the step")
+    if sink is not None:
+        _need(sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous(), "sink must be float32 [H]")
+    lib = _lib("attention_mma")
+    if ctx.is_decode:
+        width = max(int(table.shape[1]), 1)
+        small, n_chunks = _decode_attention_plan(T * -(-H // 8), width, D, _sm_count(q.device))
+        _i32(ctx.tok_seq, T, "tok_seq")
+        _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
+        _check(lib.ab_attention_decode_sink_bf16(
+            _p(q), H * D, _p(out), None, None, None, _p(pages), _p(pages), _p(table), table.shape[1], _p(ctx.tok_seq),
+            _p(ctx.kv_len), T, H, 1, D, ctypes.c_float(scale), 0, -(-width // n_chunks), n_chunks, small, None, None,
+            0, 0, 0, _p(sink), _stream()), "latent_attention_decode")
+        return out
+    _i32(ctx.tok_pos, T, "tok_pos")
+    _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+    tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H, q.device)
+    _check(lib.ab_attention_prefill_sink_bf16(
+        _p(q), H * D, _p(out), _p(pages), _p(pages), _p(table), table.shape[1], _p(ctx.tok_pos), _p(ctx.cu_q),
+        _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, 1, D, ctypes.c_float(scale), 0, _p(sink), _stream()),
+        "latent_attention_prefill")
+    return out
+
+
+LIBRARY_HEADS_MIN_ROWS = 17     # from here the per-head products of bfloat16 steps are library products
+
+
+def heads_mm_library(a, a_head_stride, K, w, out, out_head_stride, n_tokens):
+    """out[t, h, :N] = a[t, h, :K] @ w[h] for w [H, K, N], bfloat16, as one library product per head on strided
+    views (steps of many rows, where the one-warp-per-output kernel would re-read the weights per token)."""
+    H, _, N = w.shape
+    av = a[:n_tokens].view(n_tokens, H, a_head_stride)
+    ov = out[:n_tokens].view(n_tokens, H, out_head_stride)
+    for h in range(H):
+        torch.mm(av[:, h, :K], w[h], out=ov[:, h, :N])
+    _mark("library product")
     return out
 
 

@@ -41,7 +41,8 @@ class LatentAttention(Mixer):
         self.up_q = Linear(opts, Q, [(f"{prefix}.{uq}", H * (D + R))], weight_suffix=weight_suffix)
         self.out = Linear(opts, H * V, [(f"{prefix}.{o}", width)], weight_suffix=weight_suffix, out_dtype=out_dtype)
         self.q_norm = self.c_norm = self.sink = None
-        self.w_uk_t = self.w_uv = None        # [H, C, D] (transposed per head) and [H, V, C]
+        self.w_uk_t = self.w_uv = None        # [H, C, D] (transposed per head) and [H, V, C]: what the kernel reads
+        self.w_uk = self.w_uv_t = None        # [H, D, C] and [H, C, V]: the right-hand sides of library products
 
     def own_param_specs(self):
         dq, _, dkv, uk, uv, _, sink = self.names
@@ -58,8 +59,10 @@ class LatentAttention(Mixer):
         specs = self.own_param_specs()
         self.q_norm, self.c_norm = fetch(specs[0]), fetch(specs[1])
         uk, uv = fetch(specs[2]), fetch(specs[3])
-        self.w_uk_t = uk.view(self.H, self.D, self.C).transpose(1, 2).contiguous()
+        self.w_uk = uk.view(self.H, self.D, self.C).contiguous()
+        self.w_uk_t = self.w_uk.transpose(1, 2).contiguous()
         self.w_uv = uv.view(self.H, self.V, self.C).contiguous()
+        self.w_uv_t = self.w_uv.transpose(1, 2).contiguous()
         self.sink = fetch(specs[4]) if self.has_sink else None
 
     def cache_spec(self):
@@ -74,10 +77,35 @@ class LatentAttention(Mixer):
         cq = torch.empty((down.shape[0], Q), dtype=self.opts.dtype, device=dev)
         ops.latent_prep(down, Q, C, R, self.q_norm, self.c_norm, self.eps, rot, ctx, cache, cq, write_cache=write_cache)
         q = self.up_q.forward(cq, n_rows=T)
+        if ops.latent_attention_mma_supports(H, C, R, self.opts.dtype):
+            return self._forward_tensor_cores(q, rot, ctx, cache)
         q_lat = torch.empty((q.shape[0], H * (C + R)), dtype=torch.float32, device=dev)
         ops.heads_matmul(q, D + R, self.w_uk_t, q_lat, C + R, T, tail=R, rot=rot, ctx=ctx)
         o_lat = torch.empty((q.shape[0], H * C), dtype=torch.float32, device=dev)
         ops.latent_attention(q_lat, o_lat, cache, ctx, H, C, R, self.scale, self.sink)
         values = torch.empty((q.shape[0], H * V), dtype=self.opts.dtype, device=dev)
         ops.heads_matmul(o_lat, C, self.w_uv, values, V, T, ctx=ctx)
+        return self.out.forward(values, n_rows=T)
+
+    def _forward_tensor_cores(self, q, rot, ctx, cache):
+        """bfloat16, rows of up to 256 dims: the folded query and the heads' outputs are bfloat16, the attention
+        runs on the tensor-core kernels; the per-head products are library products from 17 rows on."""
+        T = ctx.n_tokens
+        H, D, R, V, C = self.H, self.D, self.R, self.V, self.C
+        Dk = C + R
+        rows, dev = q.shape[0], q.device
+        many = T >= ops.LIBRARY_HEADS_MIN_ROWS
+        q_lat = torch.empty((rows, H * Dk), dtype=torch.bfloat16, device=dev)
+        if many:
+            ops.heads_mm_library(q, D + R, D, self.w_uk, q_lat, Dk, T)
+            ops.heads_matmul(q, D + R, None, q_lat, Dk, T, tail=R, rot=rot, ctx=ctx, tail_at=C)
+        else:
+            ops.heads_matmul(q, D + R, self.w_uk_t, q_lat, Dk, T, tail=R, rot=rot, ctx=ctx)
+        o_lat = torch.empty((rows, H * Dk), dtype=torch.bfloat16, device=dev)
+        ops.latent_attention_mma(q_lat, o_lat, cache, ctx, H, C, R, self.scale, self.sink)
+        values = torch.empty((rows, H * V), dtype=torch.bfloat16, device=dev)
+        if many:
+            ops.heads_mm_library(o_lat, Dk, C, self.w_uv_t, values, V, T)
+        else:
+            ops.heads_matmul(o_lat, Dk, self.w_uv, values, V, T, ctx=ctx)
         return self.out.forward(values, n_rows=T)

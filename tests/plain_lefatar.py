@@ -104,8 +104,10 @@ def dense_ff(h, w):
     return ((g / (1.0 + np.exp(-g))) * (h @ w["up"].T)) @ w["down"].T
 
 
-def route(h, router_w, rt):
-    """(chosen experts [T, top], their weights [T, top])."""
+def route(h, router_w, rt, with_margin=False):
+    """(chosen experts [T, top], their weights [T, top]); with_margin: also, per token, how far the choice is
+    from another one, in units of the router's logits: the smaller of (last chosen - best not chosen among
+    the allowed experts) and (last kept group - best dropped group)."""
     z = h @ router_w.T
     z = z - z.max(axis=-1, keepdims=True)
     s = np.exp(z)
@@ -119,15 +121,27 @@ def route(h, router_w, rt):
     masked = np.where(np.repeat(allowed, per, axis=-1), s, -1.0)
     idx = np.argsort(-masked, axis=-1, kind="stable")[:, :top]
     wts = np.take_along_axis(s, idx, axis=-1)
-    return idx, wts / (wts.sum(axis=-1, keepdims=True) + 1e-20) * rt["scale"]
+    wts_out = wts / (wts.sum(axis=-1, keepdims=True) + 1e-20) * rt["scale"]
+    if not with_margin:
+        return idx, wts_out
+    margin = np.full(T, np.inf)
+    ranked = -np.sort(-masked, axis=-1)
+    if top < E and keep * per > top:
+        margin = np.log(ranked[:, top - 1]) - np.log(np.maximum(ranked[:, top], 1e-300))
+    if keep < G:
+        gs = -np.sort(-s.reshape(T, G, per).max(axis=-1), axis=-1)
+        margin = np.minimum(margin, np.log(gs[:, keep - 1]) - np.log(gs[:, keep]))
+    return idx, wts_out, margin
 
 
 def gelu_erf(z):
     return 0.5 * z * (1.0 + np.vectorize(math.erf)(z / math.sqrt(2.0)))
 
 
-def moe_ff(h, w, mlp):
-    idx, wts = route(h, w["router"], mlp["router"])
+def moe_ff(h, w, mlp, margins=None):
+    idx, wts, margin = route(h, w["router"], mlp["router"], with_margin=True)
+    if margins is not None:
+        margins.append(margin)
     out = np.zeros((h.shape[0], w["e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for e, g in zip(idx[t], wts[t]):
@@ -139,8 +153,9 @@ def sub(weights, prefix):
     return {k[len(prefix):]: np.asarray(v, dtype=np.float64) for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(config, weights, tokens, return_layers=False):
-    """Logits [T, vocab] of one whole sequence (and the residual stream after every layer)."""
+def forward(config, weights, tokens, return_layers=False, margins=None):
+    """Logits [T, vocab] of one whole sequence (and the residual stream after every layer).  `margins`: a list
+    that gets, for every layer with routed experts, each token's distance from another choice (see `route`)."""
     eps = config["norm"]["eps"]
     x = np.asarray(weights["embed"], dtype=np.float64)[np.asarray(tokens)]
     after = []
@@ -156,7 +171,7 @@ def forward(config, weights, tokens, return_layers=False):
         mlp = layer.get("mlp")
         if mlp is not None:
             fw = sub(weights, f"l{i}.mlp.")
-            y = y + (dense_ff(h, fw) if mlp["kind"] == "dense" else moe_ff(h, fw, mlp))
+            y = y + (dense_ff(h, fw) if mlp["kind"] == "dense" else moe_ff(h, fw, mlp, margins))
         x = x + y
         after.append(x.copy())
     logits = norm_offset(x, np.asarray(weights["final.norm"], dtype=np.float64), eps) @ \
