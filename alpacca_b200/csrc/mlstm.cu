@@ -6,13 +6,17 @@
 //   S_t = exp(gf_t + m_{t-1} - m_t) S_{t-1} + exp(gi_t - m_t) k_t v_t^T        [D, V]
 //   n_t = (the same two factors) n_{t-1}, k_t                                     [D]
 //   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6),   q_t scaled by qscale
-// Three kernels:
-//   gates    one warp per (sequence, head) walks the tokens: the two factors and the denominator of every
-//            token (n and m live here);
-//   state    one CTA per (sequence, head, tile of columns of S): each thread owns one column of S, in
-//            registers when D is 16, 32, 64 or 128 and in shared memory otherwise, and walks the tokens;
-//            columns need nothing from each other, so no barrier is inside the loop;
-//   output   per (token, head): o divided by its root mean square, times a weight, times sigmoid(gate).
+// Three kernels, in two forms.  The form for D a multiple of 16 up to 256 (rows 16-byte aligned):
+//   scan     one warp per (sequence, head): the gates of 32 tokens at a time, in parallel, the running maximum
+//            by a scan over the warp; leaves (keep, add, m) per token;
+//   state    one CTA per (sequence, head, 8 or 32 columns of [S | n]): n is one more column of S, the one whose
+//            value is 1.  A column's D entries are spread over 16 (4) threads' registers; q, k, v and the
+//            factors of 4 to 16 tokens at a time are brought to shared memory by cp.async, three buffers, so
+//            that the walk over the tokens does not wait for memory; leaves S^T q and n . q;
+//   output   per (token, head): the denominator from n . q and m, o divided by its root mean square, times a
+//            weight, times sigmoid(gate).
+// The general form (any D up to 1024): `gates` (one warp per (sequence, head) walks the tokens and keeps n) and a
+// `state` whose threads each own one whole column, in shared memory; it leaves o already divided.
 // The state of a sequence is read when the step starts and written back when it ends, so a prompt can be
 // cut anywhere and a decode step is the same code with one token.  A row of the state per (slot, head):
 // S [D][V] | n [D] | m | padding to a multiple of 4 floats.
@@ -31,8 +35,8 @@ struct MlstmArgs {
   const int* slots;        // [B]
   const int* tok_seq;      // [T], -1: a row without a sequence
   float cap, qscale;
-  float* coef;             // [T, H, 3]: keep, add, denominator
-  float* o_raw;            // [T, H, V]
+  float* coef;             // [T, H, 3]: keep, add, and the denominator (general form) or m (fast form)
+  float* o_raw;            // [T, H, V + 1]
   int write_state;
 };
 
@@ -148,7 +152,7 @@ __global__ void mlstm_state_kernel(MlstmArgs a) {
         acc += s * qq[d];
       }
     }
-    a.o_raw[((size_t)t * a.H + h) * a.V + c] = acc * a.qscale / den;
+    a.o_raw[((size_t)t * a.H + h) * (a.V + 1) + c] = acc * a.qscale / den;
   }
   if (a.write_state && live) {
     if (DR > 0) {
@@ -160,11 +164,175 @@ __global__ void mlstm_state_kernel(MlstmArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// the fast form
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__global__ void mlstm_scan_kernel(MlstmArgs a, int n_pairs) {
+  const int lane = threadIdx.x & 31;
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= n_pairs) return;
+  const int b = w / a.H, h = w - b * a.H;
+  const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
+  const int slot = a.slots[b];
+  if (slot < 0 || t1 <= t0 || a.tok_seq[t0] < 0) return;
+  float* sm_ = a.state + ((size_t)slot * a.H + h) * a.row + (size_t)a.D * a.V + a.D;
+  float m = *sm_;
+  const float bi = a.bias_i[h], bf = a.bias_f[h];
+  for (int base = t0; base < t1; base += 32) {
+    const int t = base + lane;
+    float gi = 0.f, gf = 0.f;
+    if (t < t1) {
+      const float* p = a.proj + (size_t)t * a.ld;
+      gi = a.cap * tanhf((p[a.off_i + h] + bi) / a.cap);
+      gf = log_sigmoid(a.cap * tanhf((p[a.off_f + h] + bf) / a.cap));
+    }
+    // m' = max(m + gf, gi) is the map m -> max(m + A, B); two such maps in a row are one again,
+    // (A1 + A2, max(B1 + A2, B2)), so the 32 tokens' maps are combined by a scan over the warp
+    float A = t < t1 ? gf : 0.f, B = t < t1 ? gi : -INFINITY;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float pa = __shfl_up_sync(0xffffffffu, A, o), pb = __shfl_up_sync(0xffffffffu, B, o);
+      if (lane >= o) { B = fmaxf(pb + A, B); A = pa + A; }
+    }
+    const float m_after = fmaxf(m + A, B);
+    float m_before = __shfl_up_sync(0xffffffffu, m_after, 1);
+    if (lane == 0) m_before = m;
+    m = __shfl_sync(0xffffffffu, m_after, 31);      // lanes past the end hold the identity map
+    if (t < t1) {
+      float* c = a.coef + ((size_t)t * a.H + h) * 3;
+      c[0] = expf(gf + m_before - m_after);
+      c[1] = expf(gi - m_after);
+      c[2] = m_after;
+    }
+  }
+  if (a.write_state && lane == 0) *sm_ = m;
+}
+
+// A column's D entries are spread over DG threads of a warp, DQ = D / DG each (DG 16 when D is a multiple of
+// 64, else 4); a warp holds 32 / DG columns, the CTA of four warps COLS = 128 / DG.  TB tokens per buffer.
+// Per token a thread updates its DQ entries and leaves its share of the column's dot product with q in shared
+// memory; the shares of a buffer's tokens are added after its last token, so that the walk over the tokens
+// has neither a shuffle nor a barrier in it.
+template <int DQ, int DG, int TB>
+__global__ void __launch_bounds__(128) mlstm_state_fast_kernel(MlstmArgs a) {
+  constexpr int NBUF = 3;                               // buffers of TB tokens: two are on their way while one is read
+  constexpr int D = DQ * DG;
+  constexpr int COLS = 128 / DG;
+  constexpr int SP = ((DQ / 4) & 1) ? DQ : DQ + 4;      // floats between two threads' parts: 4 x odd, no bank met twice
+  constexpr int KP = DG * SP;
+  __shared__ __align__(16) float ks[NBUF][TB][KP];
+  __shared__ __align__(16) float qs[NBUF][TB][KP];
+  __shared__ float vs[NBUF][TB][COLS];
+  __shared__ float cs[NBUF][TB][2];
+  __shared__ float part[TB][COLS][DG + 1];
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int dg = lane % DG;                         // which part of the column
+  const int col = warp * (32 / DG) + lane / DG;     // column within the CTA's COLS
+  const int c = blockIdx.z * COLS + col;            // column of [S | n]: c == V is n
+  const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
+  const int slot = a.slots[b];
+  if (slot < 0 || t1 <= t0 || a.tok_seq[t0] < 0) return;
+  const int V = a.V;
+  const bool live = c <= V;
+  float* st = a.state + ((size_t)slot * a.H + h) * a.row;
+  float* sn = st + (size_t)D * V;
+  float reg[DQ];
+#pragma unroll
+  for (int d = 0; d < DQ; ++d) {
+    const int dd = dg * DQ + d;
+    reg[d] = !live ? 0.f : (c < V ? st[(size_t)dd * V + c] : sn[dd]);
+  }
+  const int n_blocks = (t1 - t0 + TB - 1) / TB;
+  auto stage = [&](int blk) {          // every call closes one group of copies, an empty one past the end
+    const int buf = blk % NBUF;
+    const int tb0 = t0 + blk * TB;
+    const int n = blk < n_blocks ? min(TB, t1 - tb0) : 0;
+    for (int i = tid; i < n * (D / 4); i += 128) {
+      const int tok = i / (D / 4), ch = i - tok * (D / 4);
+      const int p_ = (ch * 4) / DQ, within = ch * 4 - p_ * DQ;
+      const float* p = a.proj + (size_t)(tb0 + tok) * a.ld;
+      cp_async_16(&ks[buf][tok][p_ * SP + within], p + a.off_k + h * D + ch * 4);
+      cp_async_16(&qs[buf][tok][p_ * SP + within], p + a.off_q + h * D + ch * 4);
+    }
+    for (int i = tid; i < n * COLS; i += 128) {
+      const int tok = i / COLS, cc = i - tok * COLS;
+      const int gc = blockIdx.z * COLS + cc;
+      if (gc < V) cp_async_4(&vs[buf][tok][cc], a.proj + (size_t)(tb0 + tok) * a.ld + a.off_v + h * V + gc);
+    }
+    for (int i = tid; i < n * 2; i += 128) {
+      const int tok = i >> 1, j = i & 1;
+      cp_async_4(&cs[buf][tok][j], a.coef + ((size_t)(tb0 + tok) * a.H + h) * 3 + j);
+    }
+    cp_async_commit();
+  };
+  for (int blk = 0; blk < NBUF - 1; ++blk) stage(blk);
+  for (int blk = 0; blk < n_blocks; ++blk) {
+    const int buf = blk % NBUF;
+    stage(blk + NBUF - 1);             // into the buffer that the barrier at the end of the last round set free
+    cp_async_wait<NBUF - 1>();         // all but the latest NBUF - 1 groups have landed: this round's buffer has
+    __syncthreads();
+    const int tb0 = t0 + blk * TB;
+    const int n = min(TB, t1 - tb0);
+#pragma unroll 4
+    for (int i = 0; i < n; ++i) {
+      const float keep = cs[buf][i][0], add = cs[buf][i][1];
+      const float av = !live ? 0.f : add * (c < V ? vs[buf][i][col] : 1.0f);
+      const float* kk = &ks[buf][i][dg * SP];
+      const float* qq = &qs[buf][i][dg * SP];
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int d = 0; d < DQ; d += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kk + d);
+        const float4 q4 = *reinterpret_cast<const float4*>(qq + d);
+        reg[d] = keep * reg[d] + av * k4.x;
+        acc0 += reg[d] * q4.x;
+        reg[d + 1] = keep * reg[d + 1] + av * k4.y;
+        acc1 += reg[d + 1] * q4.y;
+        reg[d + 2] = keep * reg[d + 2] + av * k4.z;
+        acc0 += reg[d + 2] * q4.z;
+        reg[d + 3] = keep * reg[d + 3] + av * k4.w;
+        acc1 += reg[d + 3] * q4.w;
+      }
+      part[i][col][dg] = acc0 + acc1;
+    }
+    __syncthreads();
+    for (int i = tid; i < n * COLS; i += 128) {
+      const int tok = i / COLS, cc = i - tok * COLS;
+      const int gc = blockIdx.z * COLS + cc;
+      if (gc <= V) {
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < DG; ++j) sum += part[tok][cc][j];
+        a.o_raw[((size_t)(tb0 + tok) * a.H + h) * (V + 1) + gc] = sum * a.qscale;
+      }
+    }
+    __syncthreads();
+  }
+  if (a.write_state && live) {
+#pragma unroll
+    for (int d = 0; d < DQ; ++d) {
+      const int dd = dg * DQ + d;
+      if (c < V) st[(size_t)dd * V + c] = reg[d]; else sn[dd] = reg[d];
+    }
+  }
+}
+
 // out[t, h*V + c] = o / rms(o over the head) * weight[h*V + c] * sigmoid(g[t, h*V + c]); one warp per (token, head)
+// raw: o_raw holds S^T q and, in column V, n . q, and coef's third number is m: the denominator is formed here.
 template <typename T>
 __global__ void mlstm_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, int ld, int off_g,
                                     const float* __restrict__ weight, const int* __restrict__ tok_seq, T* __restrict__ out,
-                                    int n_tokens, int H, int V, float eps) {
+                                    int n_tokens, int H, int V, float eps, const float* __restrict__ coef, int raw) {
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= (long long)n_tokens * H) return;
@@ -174,11 +342,13 @@ __global__ void mlstm_output_kernel(const float* __restrict__ o_raw, const float
     for (int c = lane; c < V; c += 32) y[c] = from_f32<T>(0.f);
     return;
   }
-  const float* o = o_raw + ((size_t)t * H + h) * V;
+  const float* o = o_raw + ((size_t)t * H + h) * (V + 1);
+  float scale = 1.0f;
+  if (raw) scale = 1.0f / (fmaxf(fabsf(o[V]), expf(-coef[((size_t)t * H + h) * 3 + 2])) + 1e-6f);
   float ss = 0.f;
-  for (int c = lane; c < V; c += 32) ss += o[c] * o[c];
+  for (int c = lane; c < V; c += 32) ss += (o[c] * scale) * (o[c] * scale);
   ss = warp_sum(ss);
-  const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+  const float inv = scale / sqrtf(ss / (float)V + eps);
   const float* g = proj + (size_t)t * ld + off_g + h * V;
   for (int c = lane; c < V; c += 32) {
     const float gate = 1.0f / (1.0f + expf(-g[c]));
@@ -195,6 +365,26 @@ AB_API int ab_mlstm_step(const float* proj, int ld, int off_q, int off_k, int of
   if (H <= 0 || D <= 0 || V <= 0 || D > 1024 || row < D * V + D + 1) return AB_BAD_ARG;
   MlstmArgs a{proj, ld, off_q, off_k, off_v, off_g, off_i, off_f, bias_i, bias_f, state, row, H, D, V, cu_q, slots,
               tok_seq, cap, qscale, coef, o_raw, write_state};
+  const bool fast = D % 16 == 0 && D <= 256 && off_q % 4 == 0 && off_k % 4 == 0 && ld % 4 == 0;
+  if (fast) {
+    const int pairs = n_seqs * H, wpb = 4;
+    mlstm_scan_kernel<<<(unsigned)((pairs + wpb - 1) / wpb), wpb * 32, 0, stream>>>(a, pairs);
+    int rc = ab_launch_status();
+    if (rc) return rc;
+    const int cols = D % 64 == 0 ? 8 : 32;
+    dim3 grid((unsigned)n_seqs, (unsigned)H, (unsigned)((V + 1 + cols - 1) / cols));
+    switch (D / 16) {
+#define AB_FAST(N, DQ, DG, TB) case N: mlstm_state_fast_kernel<DQ, DG, TB><<<grid, 128, 0, stream>>>(a); break;
+      AB_FAST(1, 4, 4, 16) AB_FAST(2, 8, 4, 16) AB_FAST(3, 12, 4, 16) AB_FAST(4, 4, 16, 16) AB_FAST(5, 20, 4, 8)
+      AB_FAST(6, 24, 4, 8) AB_FAST(7, 28, 4, 8) AB_FAST(8, 8, 16, 8) AB_FAST(9, 36, 4, 4) AB_FAST(10, 40, 4, 4)
+      AB_FAST(11, 44, 4, 4) AB_FAST(12, 12, 16, 8) AB_FAST(13, 52, 4, 4) AB_FAST(14, 56, 4, 4) AB_FAST(15, 60, 4, 4)
+      AB_FAST(16, 16, 16, 4)
+#undef AB_FAST
+      default: return AB_BAD_ARG;
+    }
+    rc = ab_launch_status();
+    if (rc) return rc;
+  } else {
   {
     const int pairs = n_seqs * H, wpb = 4;
     const unsigned blocks = (unsigned)((pairs + wpb - 1) / wpb);
@@ -227,16 +417,17 @@ AB_API int ab_mlstm_step(const float* proj, int ld, int off_q, int off_k, int of
     int rc = ab_launch_status();
     if (rc) return rc;
   }
+  }
   {
     const long long warps = (long long)n_tokens * H;
     const int wpb = 4;
     const unsigned blocks = (unsigned)((warps + wpb - 1) / wpb);
     if (out_dtype == AB_F32)
       mlstm_output_kernel<float><<<blocks, wpb * 32, 0, stream>>>(o_raw, proj, ld, off_g, weight, tok_seq, (float*)out,
-                                                                   n_tokens, H, V, eps);
+                                                                   n_tokens, H, V, eps, coef, fast ? 1 : 0);
     else if (out_dtype == AB_BF16)
       mlstm_output_kernel<bf16><<<blocks, wpb * 32, 0, stream>>>(o_raw, proj, ld, off_g, weight, tok_seq, (bf16*)out,
-                                                                  n_tokens, H, V, eps);
+                                                                  n_tokens, H, V, eps, coef, fast ? 1 : 0);
     else
       return AB_BAD_ARG;
   }

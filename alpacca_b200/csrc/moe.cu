@@ -11,23 +11,69 @@
 
 #define MOE_MAX_EXPERTS 1024
 
+// A warp's share of the dot product of two rows of n numbers (add with warp_sum): 16 bytes per lane and
+// load where both rows allow it.
+__device__ __forceinline__ float lane_dot(const bf16* __restrict__ a, const bf16* __restrict__ b, int n, int lane) {
+  float part = 0.f;
+  if ((n & 7) == 0 && ((((uintptr_t)a) | ((uintptr_t)b)) & 15) == 0) {
+    for (int k = lane * 8; k < n; k += 256) {
+      const uint4 x = *reinterpret_cast<const uint4*>(a + k);
+      const uint4 y = __ldg(reinterpret_cast<const uint4*>(b + k));
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+      const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = __bfloat1622float2(xp[j]), yf = __bfloat1622float2(yp[j]);
+        part += xf.x * yf.x + xf.y * yf.y;
+      }
+    }
+    return part;
+  }
+  for (int k = lane; k < n; k += 32) part += __bfloat162float(a[k]) * __bfloat162float(b[k]);
+  return part;
+}
+__device__ __forceinline__ float lane_dot(const float* __restrict__ a, const float* __restrict__ b, int n, int lane) {
+  float part = 0.f;
+  for (int k = lane; k < n; k += 32) part += a[k] * b[k];      // one order for every n: the 32-bit path
+  return part;
+}
+__device__ __forceinline__ float lane_dot(const bf16* __restrict__ a, const float* __restrict__ b, int n, int lane) {
+  float part = 0.f;
+  if ((n & 3) == 0 && (((uintptr_t)a) & 7) == 0 && (((uintptr_t)b) & 15) == 0) {
+    for (int k = lane * 4; k < n; k += 128) {
+      const uint2 x = *reinterpret_cast<const uint2*>(a + k);
+      const float4 y = __ldg(reinterpret_cast<const float4*>(b + k));
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+      const float2 x0 = __bfloat1622float2(xp[0]), x1 = __bfloat1622float2(xp[1]);
+      part += x0.x * y.x + x0.y * y.y + x1.x * y.z + x1.y * y.w;
+    }
+    return part;
+  }
+  for (int k = lane; k < n; k += 32) part += __bfloat162float(a[k]) * b[k];
+  return part;
+}
+
+// z[t, e] = W_r[e] . h[t]: one warp per (token, expert)
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ wr, int n_tokens, int width,
-                                 int E, int groups, int keep, int top, float scale, int* __restrict__ idx,
-                                 float* __restrict__ wts) {
+__global__ void moe_logits_kernel(const T* __restrict__ h, int ld, const float* __restrict__ wr, int n_tokens, int width,
+                                  int E, float* __restrict__ z) {
+  const int lane = threadIdx.x & 31;
+  const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (id >= (long long)n_tokens * E) return;
+  const int t = (int)(id / E), e = (int)(id - (long long)t * E);
+  const float part = warp_sum(lane_dot(h + (size_t)t * ld, wr + (size_t)e * width, width, lane));
+  if (lane == 0) z[id] = part;
+}
+
+// the choice, one warp per token, from the logits z [T, E]
+__global__ void moe_route_kernel(const float* __restrict__ z, int n_tokens, int E, int groups, int keep, int top,
+                                 float scale, int* __restrict__ idx, float* __restrict__ wts) {
   extern __shared__ float sm[];           // E scores per warp, then `groups` group scores per warp
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int t = blockIdx.x * (blockDim.x >> 5) + wib;
   if (t >= n_tokens) return;
   float* s = sm + (size_t)wib * E;
-  const T* x = h + (size_t)t * ld;
-  for (int e = 0; e < E; ++e) {
-    const float* w = wr + (size_t)e * width;
-    float part = 0.f;
-    for (int k = lane; k < width; k += 32) part += to_f32(x[k]) * w[k];
-    part = warp_sum(part);
-    if (lane == 0) s[e] = part;
-  }
+  for (int e = lane; e < E; e += 32) s[e] = z[(size_t)t * E + e];
   __syncwarp();
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
@@ -100,22 +146,25 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int ld, const float* _
 }
 
 AB_API int ab_moe_route(const void* h, int dtype, int ld, const float* wr, int n_tokens, int width, int E, int groups,
-                        int keep, int top, float scale, int* idx, float* wts, cudaStream_t stream) {
+                        int keep, int top, float scale, float* z, int* idx, float* wts, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (E <= 0 || E > MOE_MAX_EXPERTS || groups <= 0 || E % groups || keep <= 0 || keep > groups || top <= 0 ||
       top > keep * (E / groups))
     return AB_BAD_ARG;
   const int wpb = 4;
-  const unsigned blocks = (unsigned)((n_tokens + wpb - 1) / wpb);
-  const size_t smem = (size_t)wpb * (E + groups) * sizeof(float);
+  const long long lw = (long long)n_tokens * E;
+  const unsigned lblocks = (unsigned)((lw + 7) / 8);
   if (dtype == AB_F32)
-    moe_route_kernel<float><<<blocks, wpb * 32, smem, stream>>>((const float*)h, ld, wr, n_tokens, width, E, groups,
-                                                                 keep, top, scale, idx, wts);
+    moe_logits_kernel<float><<<lblocks, 256, 0, stream>>>((const float*)h, ld, wr, n_tokens, width, E, z);
   else if (dtype == AB_BF16)
-    moe_route_kernel<bf16><<<blocks, wpb * 32, smem, stream>>>((const bf16*)h, ld, wr, n_tokens, width, E, groups, keep,
-                                                                top, scale, idx, wts);
+    moe_logits_kernel<bf16><<<lblocks, 256, 0, stream>>>((const bf16*)h, ld, wr, n_tokens, width, E, z);
   else
     return AB_BAD_ARG;
+  int rc = ab_launch_status();
+  if (rc) return rc;
+  const unsigned blocks = (unsigned)((n_tokens + wpb - 1) / wpb);
+  const size_t smem = (size_t)wpb * (E + groups) * sizeof(float);
+  moe_route_kernel<<<blocks, wpb * 32, smem, stream>>>(z, n_tokens, E, groups, keep, top, scale, idx, wts);
   return ab_launch_status();
 }
 
@@ -132,20 +181,18 @@ __global__ void moe_up_pairs_kernel(const T* __restrict__ h, int ld, const T* __
   const int p = (int)(id / ff), j = (int)(id - (long long)p * ff);
   const int e = idx[p];
   const T* x = h + (size_t)(p / top) * ld;
-  const T* w = w_up + ((size_t)e * ff + j) * width;
-  float part = 0.f;
-  for (int k = lane; k < width; k += 32) part += to_f32(x[k]) * to_f32(w[k]);
-  part = warp_sum(part);
+  const float part = warp_sum(lane_dot(x, w_up + ((size_t)e * ff + j) * width, width, lane));
   if (lane == 0) {
     act[(size_t)p * ff + j] = from_f32<T>(activation == 0 ? gelu_erf(part) : silu(part));
   }
 }
 
 // out[t, i] = sum_k wts[t, k] * (W_down[e_k][i] . act[t * top + k]).  One warp per (token, i).
+// w_down: [width, E, ff], the experts side by side in a row (the layout of one product over all experts).
 template <typename T>
 __global__ void moe_down_pairs_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ idx,
                                       const float* __restrict__ wts, T* __restrict__ out, int n_tokens, int top, int width,
-                                      int ff) {
+                                      int ff, int E) {
   const int lane = threadIdx.x & 31;
   const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (id >= (long long)n_tokens * width) return;
@@ -153,10 +200,7 @@ __global__ void moe_down_pairs_kernel(const T* __restrict__ act, const T* __rest
   float total = 0.f;
   for (int k = 0; k < top; ++k) {
     const int e = idx[(size_t)t * top + k];
-    const T* a = act + ((size_t)t * top + k) * ff;
-    const T* w = w_down + ((size_t)e * width + i) * ff;
-    float part = 0.f;
-    for (int j = lane; j < ff; j += 32) part += to_f32(a[j]) * to_f32(w[j]);
+    const float part = lane_dot(act + ((size_t)t * top + k) * ff, w_down + ((size_t)i * E + e) * ff, ff, lane);
     total += wts[(size_t)t * top + k] * warp_sum(part);
   }
   if (lane == 0) out[(size_t)t * width + i] = from_f32<T>(total);
@@ -175,14 +219,81 @@ AB_API int ab_moe_pairs(const void* h, int dtype, int ld, const void* w_up, cons
     moe_up_pairs_kernel<float><<<(unsigned)up_blocks, wpb * 32, 0, stream>>>(
         (const float*)h, ld, (const float*)w_up, idx, (float*)act, n_tokens * top, top, width, ff, activation);
     moe_down_pairs_kernel<float><<<(unsigned)down_blocks, wpb * 32, 0, stream>>>(
-        (const float*)act, (const float*)w_down, idx, wts, (float*)out, n_tokens, top, width, ff);
+        (const float*)act, (const float*)w_down, idx, wts, (float*)out, n_tokens, top, width, ff, E);
   } else if (dtype == AB_BF16) {
     moe_up_pairs_kernel<bf16><<<(unsigned)up_blocks, wpb * 32, 0, stream>>>(
         (const bf16*)h, ld, (const bf16*)w_up, idx, (bf16*)act, n_tokens * top, top, width, ff, activation);
     moe_down_pairs_kernel<bf16><<<(unsigned)down_blocks, wpb * 32, 0, stream>>>(
-        (const bf16*)act, (const bf16*)w_down, idx, wts, (bf16*)out, n_tokens, top, width, ff);
+        (const bf16*)act, (const bf16*)w_down, idx, wts, (bf16*)out, n_tokens, top, width, ff, E);
   } else {
     return AB_BAD_ARG;
   }
+  return ab_launch_status();
+}
+
+// All experts at once, for steps of many tokens: up[t, e * ff + j] holds W_up[e][j] . h[t] for every expert
+// (one product); in place it becomes act(up) * (the token's weight for expert e, 0 if e was not chosen), so
+// that one product with the experts side by side, [width, E * ff], adds the chosen experts' outputs.
+template <typename T>
+__global__ void moe_weigh_all_kernel(T* __restrict__ up, const int* __restrict__ idx, const float* __restrict__ wts,
+                                     int n_tokens, int top, int ff, int E, int activation) {
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;       // column in [0, E * ff)
+  if (c >= E * ff) return;
+  const int e = c / ff;
+  float g = 0.f;
+  for (int k = 0; k < top; ++k)
+    if (idx[(size_t)t * top + k] == e) g = wts[(size_t)t * top + k];
+  T* x = up + (size_t)t * E * ff + c;
+  float y = 0.f;
+  if (g != 0.f) {
+    const float z = to_f32(*x);
+    y = g * (activation == 0 ? gelu_erf(z) : silu(z));
+  }
+  *x = from_f32<T>(y);
+}
+
+// the same, eight bfloat16 columns per thread (ff a multiple of 8: the eight belong to one expert); the columns
+// of experts that were not chosen are written without being read
+__global__ void moe_weigh_all_bf16x8_kernel(bf16* __restrict__ up, const int* __restrict__ idx,
+                                            const float* __restrict__ wts, int n_tokens, int top, int ff, int E,
+                                            int activation) {
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= E * ff) return;
+  const int e = c / ff;
+  float g = 0.f;
+  for (int k = 0; k < top; ++k)
+    if (idx[(size_t)t * top + k] == e) g = wts[(size_t)t * top + k];
+  uint4* x = reinterpret_cast<uint4*>(up + (size_t)t * E * ff + c);
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (g != 0.f) {
+    v = *x;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 z = __bfloat1622float2(p[j]);
+      z.x = g * (activation == 0 ? gelu_erf(z.x) : silu(z.x));
+      z.y = g * (activation == 0 ? gelu_erf(z.y) : silu(z.y));
+      p[j] = __floats2bfloat162_rn(z.x, z.y);
+    }
+  }
+  *x = v;
+}
+
+AB_API int ab_moe_weigh_all(void* up, int dtype, const int* idx, const float* wts, int n_tokens, int top, int ff, int E,
+                            int activation, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (top <= 0 || ff <= 0 || E <= 0 || n_tokens > 65535 || (activation != 0 && activation != 1)) return AB_BAD_ARG;
+  dim3 grid((unsigned)(((long long)E * ff + 255) / 256), (unsigned)n_tokens);
+  if (dtype == AB_F32)
+    moe_weigh_all_kernel<float><<<grid, 256, 0, stream>>>((float*)up, idx, wts, n_tokens, top, ff, E, activation);
+  else if (dtype == AB_BF16 && ff % 8 == 0 && (((uintptr_t)up) & 15) == 0) {
+    dim3 grid8((unsigned)(((long long)E * ff / 8 + 255) / 256), (unsigned)n_tokens);
+    moe_weigh_all_bf16x8_kernel<<<grid8, 256, 0, stream>>>((bf16*)up, idx, wts, n_tokens, top, ff, E, activation);
+  } else if (dtype == AB_BF16)
+    moe_weigh_all_kernel<bf16><<<grid, 256, 0, stream>>>((bf16*)up, idx, wts, n_tokens, top, ff, E, activation);
+  else
+    return AB_BAD_ARG;
   return ab_launch_status();
 }

@@ -957,7 +957,7 @@ def mlstm_step(proj, offsets, bias_i, bias_f, state, ctx, H, D, V, cap, qscale, 
     _i32(ctx.slots, B, "slots")
     _i32(ctx.tok_seq, T, "tok_seq")
     coef = torch.empty((T, H, 3), dtype=torch.float32, device=proj.device)
-    o_raw = torch.empty((T, H, V), dtype=torch.float32, device=proj.device)
+    o_raw = torch.empty((T, H, V + 1), dtype=torch.float32, device=proj.device)
     _check(_lib("mlstm").ab_mlstm_step(
         _p(proj), ld, off_q, off_k, off_v, off_g, off_i, off_f, _p(bias_i), _p(bias_f), _p(state), row, H, D, V,
         _p(ctx.cu_q), _p(ctx.slots), _p(ctx.tok_seq), B, T, ctypes.c_float(cap), ctypes.c_float(qscale), _p(coef),
@@ -1131,23 +1131,38 @@ def moe_route(h, router, n_tokens, groups, keep, top, scale):
           f"moe_route: {E} experts in {groups} groups, {keep} kept, {top} chosen cannot be routed")
     idx = torch.empty((max(n_tokens, 1), top), dtype=torch.int32, device=h.device)
     wts = torch.empty((max(n_tokens, 1), top), dtype=torch.float32, device=h.device)
+    z = torch.empty((max(n_tokens, 1), E), dtype=torch.float32, device=h.device)
     _check(_lib("moe").ab_moe_route(_p(h), _dt(h), width, _p(router), n_tokens, width, E, groups, keep, top,
-                                    ctypes.c_float(scale), _p(idx), _p(wts), _stream()), "moe_route")
+                                    ctypes.c_float(scale), _p(z), _p(idx), _p(wts), _stream()), "moe_route")
     return idx, wts
 
 
+MOE_ALL_EXPERTS_MIN_ROWS = 33      # from here a bfloat16 step runs every expert on every token in two library
+#                                    products (weights of experts that were not chosen are zero) instead of reading
+#                                    the chosen experts' rows once per (token, expert) pair
+
+
 def moe_experts(h, w_up, w_down, idx, wts, out, n_tokens, activation="gelu"):
-    """out[t] = sum_j wts[t, j] * w_down[idx[t, j]] @ act(w_up[idx[t, j]] @ h[t]); w_up [E, ff, width],
-    w_down [E, width, ff], all of h's dtype."""
+    """out[t] = sum_j wts[t, j] * W_down[idx[t, j]] @ act(W_up[idx[t, j]] @ h[t]); w_up [E, ff, width],
+    w_down [width, E, ff] (the experts side by side), all of h's dtype."""
     _cuda(h, w_up, w_down, idx, wts, out)
     E, ff, width = w_up.shape
     top = idx.shape[-1]
-    _need(tuple(w_down.shape) == (E, width, ff) and w_up.is_contiguous() and w_down.is_contiguous()
-          and w_up.dtype == h.dtype and w_down.dtype == h.dtype, "moe_experts: w_up [E, ff, width], w_down [E, width, ff]")
+    _need(tuple(w_down.shape) == (width, E, ff) and w_up.is_contiguous() and w_down.is_contiguous()
+          and w_up.dtype == h.dtype and w_down.dtype == h.dtype, "moe_experts: w_up [E, ff, width], w_down [width, E, ff]")
     _need(h.is_contiguous() and h.shape[-1] == width and out.is_contiguous() and out.shape[-1] == width
           and out.dtype == h.dtype and out.numel() >= n_tokens * width, "moe_experts: h, out [T, width] of one dtype")
     _i32(idx, n_tokens * top, "experts")
     _need(wts.dtype == torch.float32 and wts.is_contiguous() and wts.numel() >= n_tokens * top, "weights float32 [T, top]")
+    if h.dtype == torch.bfloat16 and MOE_ALL_EXPERTS_MIN_ROWS <= n_tokens <= 65535:
+        up = torch.empty((n_tokens, E * ff), dtype=h.dtype, device=h.device)
+        torch.mm(h[:n_tokens], w_up.view(E * ff, width).t(), out=up)
+        _mark("library product")
+        _check(_lib("moe").ab_moe_weigh_all(_p(up), _dt(up), _p(idx), _p(wts), n_tokens, top, ff, E,
+                                            MOE_ACTIVATIONS[activation], _stream()), "moe_weigh_all")
+        torch.mm(up, w_down.view(width, E * ff).t(), out=out[:n_tokens])
+        _mark("library product")
+        return out
     act = torch.empty((max(n_tokens, 1) * top, ff), dtype=h.dtype, device=h.device)
     _check(_lib("moe").ab_moe_pairs(_p(h), _dt(h), width, _p(w_up), _p(w_down), _p(idx), _p(wts), _p(act), _p(out),
                                     n_tokens, top, width, ff, E, MOE_ACTIVATIONS[activation], _stream()), "moe_experts")

@@ -6,9 +6,11 @@
     weights = chosen s / (their sum + 1e-20) * scale;  output = sum of weight * expert(h)
     expert(h) = W_down act(W_up h), no biases
 
-The experts' matrices are stacked ([experts, ff, width] and [experts, width, ff]) so that a kernel picks an
-expert by index from device memory: routing never reaches the host, and a step with routed experts is
-captured in a CUDA graph like any other (csrc/moe.cu).
+The experts' matrices are stacked ([experts, ff, width] and, side by side, [width, experts, ff]) so that a
+kernel picks an expert by index from device memory: routing never reaches the host, and a step with routed
+experts is captured in a CUDA graph like any other (csrc/moe.cu).  Steps of few tokens read the chosen
+experts' rows per (token, expert) pair; steps of many tokens run all experts in two library products with the
+weights of experts that were not chosen set to zero (`ops.moe_experts`).
 """
 from __future__ import annotations
 
@@ -44,7 +46,7 @@ class RoutedExperts(FeedForward):
         specs = self.own_param_specs()
         self.router = fetch(specs[0])
         self.w_up = torch.stack([fetch(s) for s in specs[1::2]]).contiguous()
-        self.w_down = torch.stack([fetch(s) for s in specs[2::2]]).contiguous()
+        self.w_down = torch.stack([fetch(s) for s in specs[2::2]], dim=1).contiguous()      # [width, E, ff]
 
     def forward(self, h, ctx):
         T = ctx.n_tokens

@@ -28,6 +28,10 @@ them out).
 `--impl reference` runs the same workload through the unmodified reference (a CPU engine for one
 sequence at a time: it takes the sequences one after another) and prints the same line.
 
+`--design lefatar` leaves the workload above alone and measures the Lefatar decoder (matrix-memory and
+latent-attention layers, dense and routed feed-forwards) beside the Llama decoder of the same width, depth and
+dense feed-forward: one prompt of 2,048 tokens and decode at batch 8 from 512-token prompts, at two sizes.
+
 One JSON line goes to standard output.  With --gpus N > 1 it prints a line that says so and exits
 with 2: this library runs on one GPU.
 """
@@ -532,6 +536,108 @@ def run_reference(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --design lefatar: the Lefatar decoder beside the Llama decoder of the same width, depth and dense
+# feed-forward, at sizes that resemble a real model's layers (random weights).
+
+def _lefatar_layers(E, mlstm, latent, dense_ff, moe, n_layers):
+    """The pattern (memory + dense, memory + experts, latent attention + dense, memory + experts), repeated."""
+    dense = {"kind": "dense", "ff": dense_ff}
+    pattern = [{"type": "mlstm", "mixer": mlstm, "mlp": dense}, {"type": "mlstm", "mixer": mlstm, "mlp": moe},
+               {"type": "latent_attention", "mixer": latent, "mlp": dense}, {"type": "mlstm", "mixer": mlstm, "mlp": moe}]
+    return [pattern[i % 4] for i in range(n_layers)]
+
+
+def _moe(ff, experts, top, count, keep):
+    return {"kind": "moe", "expert": {"ff": ff},
+            "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": count, "keep": keep}}}
+
+
+DESIGN_SIZES = {
+    "w1024": {"width": 1024, "layers": 8, "vocab": 32000, "dense_ff": 2816, "heads": 16, "kv_heads": 4, "head_dim": 64,
+              "mlstm": {"heads": 4, "dim": 128, "vdim": 256, "gate_cap": 15.0},
+              "latent": {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "q_rank": 384, "kv_rank": 224,
+                         "scale": 96 ** -0.5, "rot": {"base": 10000.0, "dims": 32}},
+              "moe": _moe(704, 8, 2, 2, 1)},
+    "w2048": {"width": 2048, "layers": 8, "vocab": 32000, "dense_ff": 5632, "heads": 16, "kv_heads": 4, "head_dim": 128,
+              "mlstm": {"heads": 8, "dim": 128, "vdim": 256, "gate_cap": 15.0},
+              "latent": {"heads": 16, "dim": 128, "rot_dim": 32, "vdim": 128, "q_rank": 768, "kv_rank": 224,
+                         "scale": 160 ** -0.5, "rot": {"base": 10000.0, "dims": 32}},
+              "moe": _moe(1408, 16, 4, 4, 2)},
+}
+
+
+def design_configs(size):
+    z = DESIGN_SIZES[size]
+    lefatar = {"architecture": "Lefatar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+               "layers": _lefatar_layers(z["width"], z["mlstm"], z["latent"], z["dense_ff"], z["moe"], z["layers"])}
+    llama = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": z["layers"], "hidden_size": z["width"],
+             "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["head_dim"],
+             "intermediate_size": z["dense_ff"], "vocab_size": z["vocab"], "max_position_embeddings": 8192,
+             "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "rope_pairing": "neox", "tie_word_embeddings": False,
+             "hidden_act": "silu"}
+    return {"lefatar": lefatar, "llama": llama}
+
+
+def op_table(model, entries):
+    """{operation: [launches, microseconds]} of one step issued launch by launch."""
+    from alpacca_b200 import ops
+    with ops.timers() as t:
+        model.engine.step(entries)
+    return {k: [n, round(us, 1)] for k, (n, us) in sorted(t.totals().items(), key=lambda kv: -kv[1][1])}
+
+
+def run_design(args):
+    import torch
+    from alpacca_b200.api import Model
+    from alpacca_b200.engine.step import StepEntry
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(0)
+    pk = peaks()
+    batch, prompt_len, prefill_tokens = args.batch or 8, args.prompt_len or 512, args.prefill_tokens or 2048
+    steps = args.steps or 64
+    out = {"design": args.design, "batch": batch, "prompt_len": prompt_len, "prefill_tokens": prefill_tokens,
+           "decode_steps": steps, "dtype": "bf16", "data": "synthetic: uniform-random token ids, random-init weights",
+           "peaks": pk, "sizes": {}}
+    for size in ([args.size] if args.size else sorted(DESIGN_SIZES)):
+        row = {}
+        for name, cfg in design_configs(size).items():
+            vocab = cfg.get("vocab") or cfg["vocab_size"]
+            shape = {"config": {"vocab_size": vocab}, "prompt_lengths": (prompt_len, prompt_len), "temperature": 0.0}
+            context = max(prefill_tokens, prompt_len + steps + max(args.warmup, 3) + 2)
+            model = Model.random(cfg, seed=0, n_ctx=context, dtype="bfloat16", max_batch=batch)
+            weights = model_bytes(model)
+            long_prompt = workload_prompts(dict(shape, prompt_lengths=(prefill_tokens, prefill_tokens)), 1, 7)
+            ms = measure_prefill(model, long_prompt)
+            tps, ms_step, held, kernels = measure_decode(model, shape, batch, steps, args.warmup)
+            kv = sum(g.bytes_per_token for g in model.engine.cache.kv_groups)
+            state = sum(g.state[:, 0].numel() * 4 for g in model.engine.cache.state_groups)     # per sequence
+            step_bytes = weights + held * kv + 2 * batch * state
+            res = {"parameters_m": round(model.decoder.n_params() / 1e6, 1), "weight_bytes": weights,
+                   "prefill": {"tok_s": round(prefill_tokens / (ms / 1e3), 1), "ms": round(ms, 3)},
+                   "decode": {"tok_s": round(tps, 1), "ms_per_step": round(ms_step, 4), "kernels_per_step": kernels,
+                              "bytes_per_step": int(step_bytes),
+                              "of_hbm_peak": round(step_bytes / (ms_step / 1e3) / 1e9 / pk["hbm_gbs"], 3)}}
+            if args.ops:
+                eng = model.engine
+                s = eng.alloc_slot()
+                res["prefill_ops_us"] = op_table(model, [StepEntry(s, long_prompt[0], [prefill_tokens - 1])])
+                eng.free_slot(s)
+                slots = [eng.alloc_slot() for _ in range(batch)]
+                prompts = workload_prompts(shape, batch, 3)
+                eng.step([StepEntry(a, q, []) for a, q in zip(slots, prompts)])
+                res["decode_ops_us"] = op_table(model, [StepEntry(a, [1], [0]) for a in slots])
+                for a in slots:
+                    eng.free_slot(a)
+            row[name] = res
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -550,6 +656,11 @@ def main():
                     help="with --only decode: equal prompts of this many tokens instead of the workload's")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="with --only prefill: one prompt of this many tokens instead of the workload's")
+    ap.add_argument("--design", default="", choices=["", "lefatar"],
+                    help="instead of the benchmark workload: prefill and decode throughput of this design beside the "
+                         "Llama decoder of the same width and depth (random weights), one JSON line")
+    ap.add_argument("--size", default="", choices=[""] + sorted(DESIGN_SIZES), help="with --design: one size only")
+    ap.add_argument("--ops", action="store_true", help="with --design: device time per kind of operation as well")
     args = ap.parse_args()
     n = int(os.environ.get("WORLD_SIZE", args.gpus))
     if args.gpus > 1 or n > 1:
@@ -557,6 +668,8 @@ def main():
             print(json.dumps({"impl": args.impl, "n_gpus": max(args.gpus, n),
                               "unsupported": "alpacca_b200 is a single-GPU library; bench.py runs with --gpus 1 only"}))
         return 2
+    if args.design:
+        return run_design(args)
     return run_reference(args) if args.impl == "reference" else run_ours(args)
 
 

@@ -53,7 +53,13 @@ def check(got, name, tokens, dtype, what, rows=None):
         clear = margin > CLOSE_CALL
         assert len(clear) < 20 or clear.mean() > 0.8, "too few positions with a clear choice of experts"
         got, want = got[clear], want[clear]
-    check_logits(got, want, dtype, what)
+        check_logits(got, want, dtype, what)
+        return
+    # 32-bit: sums of float32 roundings through gates, denominators and head norms that divide by small numbers
+    # in places; logits of order 1
+    diff = np.abs(np.asarray(got, np.float64) - want)
+    assert got.shape == want.shape and np.isfinite(got).all(), what
+    assert diff.max() <= 2e-4 and diff.mean() <= 1e-5, f"{what}: max |diff| {diff.max():.3e}, mean {diff.mean():.3e}"
 
 
 def some_tokens(name, n, seed):
