@@ -2,7 +2,9 @@
 (alpacca/model.py:510-514; SiLU on the gate, g/(1+exp(-g)), alpacca/tensor.py:150-160).
 
 gate and up are held as one matrix, interleaved in groups of 8 rows, so that
-one product feeds the activation kernel.
+one product feeds the activation kernel.  An inner width that is no multiple of
+8 is padded with zero rows (and zero columns of the down matrix) when the
+weights are loaded: silu(0) * 0 adds nothing.
 """
 from __future__ import annotations
 
@@ -14,15 +16,12 @@ class SwiGLU(FeedForward):
     def __init__(self, opts: BuildOptions, width: int, inner: int, prefix: str, bias: bool = False,
                  names=("gate_proj", "up_proj", "down_proj"), weight_suffix: str = ".weight",
                  out_dtype=None):
-        if inner % 8:
-            raise ValueError(f"feed-forward width {inner} must be a multiple of 8 "
-                             "(gate and up rows are interleaved in groups of 8)")
         self.opts, self.width, self.inner = opts, int(width), int(inner)
         g, u, d = names
         self.gate_up = Linear(opts, width, [(f"{prefix}.{g}", inner), (f"{prefix}.{u}", inner)], bias=bias,
-                              interleave8=True, weight_suffix=weight_suffix)
+                              interleave8=True, weight_suffix=weight_suffix, pad_rows_to=8)
         self.down = Linear(opts, inner, [(f"{prefix}.{d}", width)], bias=bias, weight_suffix=weight_suffix,
-                           out_dtype=out_dtype)
+                           out_dtype=out_dtype, pad_in_to=8)
 
     adds_to_residual = True
 

@@ -17,16 +17,23 @@ from .base import BuildOptions, OwedNorm, Part
 
 class Linear(Part):
     def __init__(self, opts: BuildOptions, in_features: int, sources, bias: bool = False,
-                 interleave8: bool = False, out_dtype: torch.dtype | None = None, weight_suffix: str = ".weight"):
+                 interleave8: bool = False, out_dtype: torch.dtype | None = None, weight_suffix: str = ".weight",
+                 pad_rows_to: int = 0, pad_in_to: int = 0):
         """`sources`: list of (checkpoint prefix, rows); tensors `<prefix>.weight`
         [rows, in] (and `<prefix>.bias` [rows]) are stacked in that order
         (`weight_suffix` "" for checkpoints that name a matrix by its prefix alone).
         `interleave8`: two sources of equal size are interleaved in groups of 8
         rows (8 of the first, 8 of the second, ...), the layout `ops.swiglu` reads.
-        `out_dtype` float32 gives float32 results from bfloat16 inputs (logits)."""
+        `out_dtype` float32 gives float32 results from bfloat16 inputs (logits).
+        `pad_rows_to` / `pad_in_to`: every source's rows / the inputs are padded with zeros up to a
+        multiple of that many when the matrix is loaded (the checkpoint keeps its own shapes):
+        `out_features` and `in_features` are then the padded sizes."""
         self.opts = opts
-        self.in_features = int(in_features)
-        self.sources = [(p, int(r)) for p, r in sources]
+        self.stored_in = int(in_features)
+        self.stored_sources = [(p, int(r)) for p, r in sources]
+        up = lambda n, m: -(-n // m) * m if m else n        # noqa: E731
+        self.in_features = up(self.stored_in, int(pad_in_to))
+        self.sources = [(p, up(r, int(pad_rows_to))) for p, r in self.stored_sources]
         self.out_features = sum(r for _, r in self.sources)
         self.has_bias = bool(bias)
         self.interleave8 = bool(interleave8)
@@ -40,10 +47,20 @@ class Linear(Part):
         self.bias = None
 
     def own_param_specs(self):
-        specs = [ParamSpec(f"{p}{self.weight_suffix}", (r, self.in_features), "matrix", "normal") for p, r in self.sources]
+        specs = [ParamSpec(f"{p}{self.weight_suffix}", (r, self.stored_in), "matrix", "normal")
+                 for p, r in self.stored_sources]
         if self.has_bias:
-            specs += [ParamSpec(f"{p}.bias", (r,), "vector", "normal") for p, r in self.sources]
+            specs += [ParamSpec(f"{p}.bias", (r,), "vector", "normal") for p, r in self.stored_sources]
         return specs
+
+    def _padded(self, t, rows):
+        """`t` with zero rows up to `rows` and, for a matrix, zero columns up to `in_features`."""
+        more_rows = rows - t.shape[0]
+        more_cols = self.in_features - t.shape[1] if t.dim() == 2 else 0
+        if more_rows == 0 and more_cols == 0:
+            return t
+        pad = (0, more_cols, 0, more_rows) if t.dim() == 2 else (0, more_rows)
+        return torch.nn.functional.pad(t, pad).contiguous()
 
     def _stack(self, tensors):
         if len(tensors) == 1:
@@ -55,10 +72,11 @@ class Linear(Part):
         return torch.cat(tensors, dim=0).contiguous()
 
     def load_own(self, fetch):
-        self.weight = self._stack([fetch(ParamSpec(f"{p}{self.weight_suffix}", (r, self.in_features), "matrix"))
-                                   for p, r in self.sources])
+        self.weight = self._stack([self._padded(fetch(ParamSpec(f"{p}{self.weight_suffix}", (r, self.stored_in), "matrix")), rp)
+                                   for (p, r), (_, rp) in zip(self.stored_sources, self.sources)])
         if self.has_bias:
-            self.bias = self._stack([fetch(ParamSpec(f"{p}.bias", (r,), "vector")) for p, r in self.sources])
+            self.bias = self._stack([self._padded(fetch(ParamSpec(f"{p}.bias", (r,), "vector")), rp)
+                                     for (p, r), (_, rp) in zip(self.stored_sources, self.sources)])
 
     def share_weight(self, tensor: torch.Tensor):
         """Uses an existing tensor as the matrix (a tied head)."""

@@ -3,7 +3,8 @@
 The configurations differ from each other in every size and constant; none of the sizes that a layer kind
 shares with another is equal by accident (value sizes, rotated and unrotated dims, widths and feed-forward
 widths differ), the rotation covers part of the rotated dims in one layer and all of them in another, groups
-of experts are 1, 2 and 3 with 1 or 2 kept, 1 to 3 experts chosen, and one layer has no feed-forward.
+of experts are 1, 2 and 3 with 1 or 2 kept, 1 to 3 experts chosen, one layer has no feed-forward, and one
+dense feed-forward has an inner width that is no multiple of 8.
 
 `make_weights` draws values that a bfloat16 holds exactly, so that the plain implementation, the 32-bit
 engine and the bfloat16 engine read the same numbers.  Scales are chosen so that faults show: matrices
@@ -50,7 +51,7 @@ TINY_Q = {
         {"type": "mlstm", "mixer": _mlstm(2, 32, 48, 15.0), "mlp": _moe(32, 8, 3, 2, 1, 2.0)},
         {"type": "latent_attention", "mixer": _latent(4, 32, 16, 24, 48, 64, 0.15, 250000.0, 16),
          "mlp": {"kind": "dense", "ff": 96}},
-        {"type": "mlstm", "mixer": _mlstm(4, 64, 20, 12.0), "mlp": {"kind": "dense", "ff": 64}},
+        {"type": "mlstm", "mixer": _mlstm(4, 64, 20, 12.0), "mlp": {"kind": "dense", "ff": 60}},
     ],
 }
 
