@@ -55,7 +55,15 @@ TINY_Q = {
     ],
 }
 
-CONFIGS = {"p": TINY_P, "q": TINY_Q}
+# TINY_P's mixers with dense feed-forwards only: no router whose choice rounding could tip, so that bfloat16
+# runs are held to the plain implementation at every position
+TINY_R = {
+    "architecture": "Lefatar", "vocab": 113, "width": 48, "norm": {"eps": 1e-5},
+    "layers": [dict(TINY_P["layers"][0]), dict(TINY_P["layers"][1], mlp={"kind": "dense", "ff": 40}),
+               dict(TINY_P["layers"][2]), dict(TINY_P["layers"][3], mlp={"kind": "dense", "ff": 52})],
+}
+
+CONFIGS = {"p": TINY_P, "q": TINY_Q, "r": TINY_R}
 
 
 def bf16_exact(x):
