@@ -11,6 +11,7 @@
 //                   rotated dims copied behind it (the query's rotated part);
 //   latent_attention_simt   one warp per (token, head) walks the keys in order (online softmax).
 #include "common.cuh"
+#include "launch.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // x: [T, ld] float32 = q latent (Q dims) | c (C dims) | r (R dims).  One block per token.
@@ -22,6 +23,8 @@ __global__ void latent_prep_kernel(const float* __restrict__ x, int ld, int Q, i
                                    const int* __restrict__ block_table, int table_width, int page_size,
                                    TA* __restrict__ pages, TA* __restrict__ cq_out, int write_cache) {
   __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int b = tok_seq[t];
   if (b < 0) return;
@@ -61,13 +64,11 @@ AB_API int ab_latent_prep(const float* x, int ld, int Q, int C, int R, const flo
   if (n_tokens <= 0) return AB_OK;
   if (Q <= 0 || C <= 0 || R < 0 || n_rot < 0 || n_rot > R || (n_rot & 1) || ld < Q + C + R) return AB_BAD_ARG;
   if (dtype == AB_F32)
-    latent_prep_kernel<float><<<n_tokens, 128, 0, stream>>>(x, ld, Q, C, R, wq, wc, eps, cos_t, sin_t, n_rot, tok_pos,
-                                                             tok_seq, block_table, table_width, page_size,
-                                                             (float*)pages, (float*)cq_out, write_cache);
+    ab_launch(latent_prep_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, x, ld, Q, C, R, wq, wc, eps, cos_t, sin_t,
+              n_rot, tok_pos, tok_seq, block_table, table_width, page_size, (float*)pages, (float*)cq_out, write_cache);
   else if (dtype == AB_BF16)
-    latent_prep_kernel<bf16><<<n_tokens, 128, 0, stream>>>(x, ld, Q, C, R, wq, wc, eps, cos_t, sin_t, n_rot, tok_pos,
-                                                            tok_seq, block_table, table_width, page_size, (bf16*)pages,
-                                                            (bf16*)cq_out, write_cache);
+    ab_launch(latent_prep_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, x, ld, Q, C, R, wq, wc, eps, cos_t, sin_t,
+              n_rot, tok_pos, tok_seq, block_table, table_width, page_size, (bf16*)pages, (bf16*)cq_out, write_cache);
   else
     return AB_BAD_ARG;
   return ab_launch_status();
@@ -82,6 +83,8 @@ __global__ void heads_matmul_kernel(const TA* __restrict__ a, int lda, int a_hs,
                                     int tail, int tail_at, const float* __restrict__ cos_t,
                                     const float* __restrict__ sin_t, int n_rot, const int* __restrict__ tok_pos,
                                     const int* __restrict__ tok_seq) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int per = N + tail;
   const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -119,9 +122,8 @@ static int heads_go(const void* a, int lda, int a_hs, const void* w, void* out, 
   const int wpb = 8;
   const long long blocks = (warps + wpb - 1) / wpb;
   if (blocks > 0x7fffffffLL) return AB_BAD_ARG;
-  heads_matmul_kernel<TA, TW, TO><<<(unsigned)blocks, wpb * 32, 0, stream>>>(
-      (const TA*)a, lda, a_hs, (const TW*)w, (TO*)out, ldo, o_hs, n_tokens, H, N, K, tail, tail_at, cos_t, sin_t, n_rot,
-      tok_pos, tok_seq);
+  ab_launch(heads_matmul_kernel<TA, TW, TO>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, (const TA*)a, lda, a_hs,
+            (const TW*)w, (TO*)out, ldo, o_hs, n_tokens, H, N, K, tail, tail_at, cos_t, sin_t, n_rot, tok_pos, tok_seq);
   return ab_launch_status();
 }
 
@@ -158,6 +160,8 @@ __global__ void latent_attention_simt_kernel(const float* __restrict__ q, float*
                                              int table_width, const int* __restrict__ tok_pos,
                                              const int* __restrict__ tok_seq, const float* __restrict__ sink,
                                              int n_tokens, int H, int C, int R, int page_size, float scale) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= (long long)n_tokens * H) return;

@@ -22,6 +22,7 @@
 // S [D][V] | n [D] | m | padding to a multiple of 4 floats.
 // The projections come as one float32 row per token: q | k | v | g | zi | zf at given offsets.
 #include "common.cuh"
+#include "launch.cuh"
 
 struct MlstmArgs {
   const float* proj;       // [T, ld]
@@ -177,6 +178,8 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __global__ void mlstm_scan_kernel(MlstmArgs a, int n_pairs) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= n_pairs) return;
@@ -234,6 +237,8 @@ __global__ void __launch_bounds__(128) mlstm_state_fast_kernel(MlstmArgs a) {
   __shared__ float vs[NBUF][TB][COLS];
   __shared__ float cs[NBUF][TB][2];
   __shared__ float part[TB][COLS][DG + 1];
+  pdl_wait();
+  pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int dg = lane % DG;                         // which part of the column
@@ -333,6 +338,8 @@ template <typename T>
 __global__ void mlstm_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, int ld, int off_g,
                                     const float* __restrict__ weight, const int* __restrict__ tok_seq, T* __restrict__ out,
                                     int n_tokens, int H, int V, float eps, const float* __restrict__ coef, int raw) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= (long long)n_tokens * H) return;
@@ -368,13 +375,14 @@ AB_API int ab_mlstm_step(const float* proj, int ld, int off_q, int off_k, int of
   const bool fast = D % 16 == 0 && D <= 256 && off_q % 4 == 0 && off_k % 4 == 0 && ld % 4 == 0;
   if (fast) {
     const int pairs = n_seqs * H, wpb = 4;
-    mlstm_scan_kernel<<<(unsigned)((pairs + wpb - 1) / wpb), wpb * 32, 0, stream>>>(a, pairs);
+    ab_launch(mlstm_scan_kernel, dim3((unsigned)((pairs + wpb - 1) / wpb)), dim3(wpb * 32), 0, stream, a, pairs);
     int rc = ab_launch_status();
     if (rc) return rc;
     const int cols = D % 64 == 0 ? 8 : 32;
     dim3 grid((unsigned)n_seqs, (unsigned)H, (unsigned)((V + 1 + cols - 1) / cols));
     switch (D / 16) {
-#define AB_FAST(N, DQ, DG, TB) case N: mlstm_state_fast_kernel<DQ, DG, TB><<<grid, 128, 0, stream>>>(a); break;
+#define AB_FAST(N, DQ, DG, TB) \
+  case N: ab_launch(mlstm_state_fast_kernel<DQ, DG, TB>, grid, dim3(128), 0, stream, a); break;
       AB_FAST(1, 4, 4, 16) AB_FAST(2, 8, 4, 16) AB_FAST(3, 12, 4, 16) AB_FAST(4, 4, 16, 16) AB_FAST(5, 20, 4, 8)
       AB_FAST(6, 24, 4, 8) AB_FAST(7, 28, 4, 8) AB_FAST(8, 8, 16, 8) AB_FAST(9, 36, 4, 4) AB_FAST(10, 40, 4, 4)
       AB_FAST(11, 44, 4, 4) AB_FAST(12, 12, 16, 8) AB_FAST(13, 52, 4, 4) AB_FAST(14, 56, 4, 4) AB_FAST(15, 60, 4, 4)
@@ -423,11 +431,11 @@ AB_API int ab_mlstm_step(const float* proj, int ld, int off_q, int off_k, int of
     const int wpb = 4;
     const unsigned blocks = (unsigned)((warps + wpb - 1) / wpb);
     if (out_dtype == AB_F32)
-      mlstm_output_kernel<float><<<blocks, wpb * 32, 0, stream>>>(o_raw, proj, ld, off_g, weight, tok_seq, (float*)out,
-                                                                   n_tokens, H, V, eps, coef, fast ? 1 : 0);
+      ab_launch(mlstm_output_kernel<float>, dim3(blocks), dim3(wpb * 32), 0, stream, (const float*)o_raw, proj, ld, off_g,
+                weight, tok_seq, (float*)out, n_tokens, H, V, eps, (const float*)coef, fast ? 1 : 0);
     else if (out_dtype == AB_BF16)
-      mlstm_output_kernel<bf16><<<blocks, wpb * 32, 0, stream>>>(o_raw, proj, ld, off_g, weight, tok_seq, (bf16*)out,
-                                                                  n_tokens, H, V, eps, coef, fast ? 1 : 0);
+      ab_launch(mlstm_output_kernel<bf16>, dim3(blocks), dim3(wpb * 32), 0, stream, (const float*)o_raw, proj, ld, off_g,
+                weight, tok_seq, (bf16*)out, n_tokens, H, V, eps, (const float*)coef, fast ? 1 : 0);
     else
       return AB_BAD_ARG;
   }

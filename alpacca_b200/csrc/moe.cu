@@ -8,6 +8,7 @@
 // The pair kernels read each chosen expert's rows once per pair: the form for steps of few tokens, where the
 // weights stream from memory once and every token adds its experts in the order of its choices.
 #include "common.cuh"
+#include "launch.cuh"
 
 #define MOE_MAX_EXPERTS 1024
 
@@ -57,6 +58,8 @@ __device__ __forceinline__ float lane_dot(const bf16* __restrict__ a, const floa
 template <typename T>
 __global__ void moe_logits_kernel(const T* __restrict__ h, int ld, const float* __restrict__ wr, int n_tokens, int width,
                                   int E, float* __restrict__ z) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (id >= (long long)n_tokens * E) return;
@@ -69,6 +72,8 @@ __global__ void moe_logits_kernel(const T* __restrict__ h, int ld, const float* 
 __global__ void moe_route_kernel(const float* __restrict__ z, int n_tokens, int E, int groups, int keep, int top,
                                  float scale, int* __restrict__ idx, float* __restrict__ wts) {
   extern __shared__ float sm[];           // E scores per warp, then `groups` group scores per warp
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int t = blockIdx.x * (blockDim.x >> 5) + wib;
   if (t >= n_tokens) return;
@@ -155,16 +160,17 @@ AB_API int ab_moe_route(const void* h, int dtype, int ld, const float* wr, int n
   const long long lw = (long long)n_tokens * E;
   const unsigned lblocks = (unsigned)((lw + 7) / 8);
   if (dtype == AB_F32)
-    moe_logits_kernel<float><<<lblocks, 256, 0, stream>>>((const float*)h, ld, wr, n_tokens, width, E, z);
+    ab_launch(moe_logits_kernel<float>, dim3(lblocks), dim3(256), 0, stream, (const float*)h, ld, wr, n_tokens, width, E, z);
   else if (dtype == AB_BF16)
-    moe_logits_kernel<bf16><<<lblocks, 256, 0, stream>>>((const bf16*)h, ld, wr, n_tokens, width, E, z);
+    ab_launch(moe_logits_kernel<bf16>, dim3(lblocks), dim3(256), 0, stream, (const bf16*)h, ld, wr, n_tokens, width, E, z);
   else
     return AB_BAD_ARG;
   int rc = ab_launch_status();
   if (rc) return rc;
   const unsigned blocks = (unsigned)((n_tokens + wpb - 1) / wpb);
   const size_t smem = (size_t)wpb * (E + groups) * sizeof(float);
-  moe_route_kernel<<<blocks, wpb * 32, smem, stream>>>(z, n_tokens, E, groups, keep, top, scale, idx, wts);
+  ab_launch(moe_route_kernel, dim3(blocks), dim3(wpb * 32), smem, stream, (const float*)z, n_tokens, E, groups, keep, top,
+            scale, idx, wts);
   return ab_launch_status();
 }
 
@@ -175,6 +181,8 @@ __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 template <typename T>
 __global__ void moe_up_pairs_kernel(const T* __restrict__ h, int ld, const T* __restrict__ w_up, const int* __restrict__ idx,
                                     T* __restrict__ act, int n_pairs, int top, int width, int ff, int activation) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (id >= (long long)n_pairs * ff) return;
@@ -193,6 +201,8 @@ template <typename T>
 __global__ void moe_down_pairs_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ idx,
                                       const float* __restrict__ wts, T* __restrict__ out, int n_tokens, int top, int width,
                                       int ff, int E) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (id >= (long long)n_tokens * width) return;
@@ -216,15 +226,15 @@ AB_API int ab_moe_pairs(const void* h, int dtype, int ld, const void* w_up, cons
   const long long up_blocks = (up_warps + wpb - 1) / wpb, down_blocks = (down_warps + wpb - 1) / wpb;
   if (up_blocks > 0x7fffffffLL || down_blocks > 0x7fffffffLL) return AB_BAD_ARG;
   if (dtype == AB_F32) {
-    moe_up_pairs_kernel<float><<<(unsigned)up_blocks, wpb * 32, 0, stream>>>(
-        (const float*)h, ld, (const float*)w_up, idx, (float*)act, n_tokens * top, top, width, ff, activation);
-    moe_down_pairs_kernel<float><<<(unsigned)down_blocks, wpb * 32, 0, stream>>>(
-        (const float*)act, (const float*)w_down, idx, wts, (float*)out, n_tokens, top, width, ff, E);
+    ab_launch(moe_up_pairs_kernel<float>, dim3((unsigned)up_blocks), dim3(wpb * 32), 0, stream, (const float*)h, ld,
+              (const float*)w_up, idx, (float*)act, n_tokens * top, top, width, ff, activation);
+    ab_launch(moe_down_pairs_kernel<float>, dim3((unsigned)down_blocks), dim3(wpb * 32), 0, stream, (const float*)act,
+              (const float*)w_down, idx, wts, (float*)out, n_tokens, top, width, ff, E);
   } else if (dtype == AB_BF16) {
-    moe_up_pairs_kernel<bf16><<<(unsigned)up_blocks, wpb * 32, 0, stream>>>(
-        (const bf16*)h, ld, (const bf16*)w_up, idx, (bf16*)act, n_tokens * top, top, width, ff, activation);
-    moe_down_pairs_kernel<bf16><<<(unsigned)down_blocks, wpb * 32, 0, stream>>>(
-        (const bf16*)act, (const bf16*)w_down, idx, wts, (bf16*)out, n_tokens, top, width, ff, E);
+    ab_launch(moe_up_pairs_kernel<bf16>, dim3((unsigned)up_blocks), dim3(wpb * 32), 0, stream, (const bf16*)h, ld,
+              (const bf16*)w_up, idx, (bf16*)act, n_tokens * top, top, width, ff, activation);
+    ab_launch(moe_down_pairs_kernel<bf16>, dim3((unsigned)down_blocks), dim3(wpb * 32), 0, stream, (const bf16*)act,
+              (const bf16*)w_down, idx, wts, (bf16*)out, n_tokens, top, width, ff, E);
   } else {
     return AB_BAD_ARG;
   }

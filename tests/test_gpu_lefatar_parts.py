@@ -230,14 +230,17 @@ def test_router(dtype, E, groups, keep, top, scale):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,groups,keep,top,ff", [(6, 3, 2, 2, 40), (4, 1, 1, 1, 24), (8, 2, 1, 3, 33)])
-def test_routed_experts(dtype, E, groups, keep, top, ff):
+@pytest.mark.parametrize("T", [5, 50])
+def test_routed_experts(dtype, E, groups, keep, top, ff, T):
+    """5 tokens: an expert's rows are read once for the pairs that chose it (or, for widths that are no multiple
+    of 8 and in 32-bit, once per pair); 50 tokens in bfloat16: all experts in two products."""
     from types import SimpleNamespace
     from alpacca_b200.parts import RoutedExperts
     width = 48
     part = RoutedExperts(opts_of(dtype), width, ff, E, top, groups, keep, 1.7, "f")
     w = short(load_part(part, seed=E, dtype=dtype, std=0.3), "f")
-    x, x64 = hidden(np.random.default_rng(ff), 50, width, dtype)
-    out = part.forward(x, SimpleNamespace(n_tokens=50)).float().cpu().numpy()
+    x, x64 = hidden(np.random.default_rng(ff), T, width, dtype)
+    out = part.forward(x, SimpleNamespace(n_tokens=T)).float().cpu().numpy()
     mlp = {"router": {"experts": E, "top": top, "scale": 1.7, "groups": {"count": groups, "keep": keep}}}
     close(out, plain.moe_ff(x64, w, mlp), dtype, "routed experts")
 
