@@ -103,7 +103,8 @@ def cmd_show(args) -> int:
         check_names(model.param_specs(), table, where=str(folder))     # one error with everything that does not fit
         n = sum(int(__import__("math").prod(shape)) for _, shape in table.values())
         print(f"\n{config.architecture}: {len(model.spec.layers)} layers, {len(table)} tensors, "
-              f"{n / 1e6:.1f}M parameters, positions up to {config.max_positions}; "
+              f"{n / 1e6:.1f}M parameters, "
+              + (f"positions up to {config.max_positions}; " if config.max_positions else "no limit on positions; ") +
               f"every tensor the model expects is there with its shape")
         if args.tensors:
             print("\ntensors:")

@@ -283,3 +283,16 @@ def test_trace_replay(dirs, dtype, tmp_path):
     for i, w in want.items():
         got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
         check_logits(got, w, dtype, "lefatar trace replay")
+
+
+def test_run_command(dirs):
+    """`python -m alpacca_b200 run` with a Lefatar folder: two prompts as one batch, greedy, in 32-bit."""
+    name = "p"
+    prompts = [some_tokens(name, 6, 70), some_tokens(name, 2, 71)]
+    text = " / ".join(" ".join(map(str, p)) for p in prompts)
+    proc = subprocess.run([sys.executable, "-m", "alpacca_b200", "run", str(dirs[name]), text, "--temp", "0",
+                           "--repeat-penalty", "1.0", "--n-predict", "5", "--dtype", "float32", "--ctx", "64"],
+                          capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [ln for ln in proc.stdout.splitlines() if ln.strip()]
+    assert [[int(t) for t in ln.split()] for ln in lines] == [plain_greedy(name, p, 5) for p in prompts]

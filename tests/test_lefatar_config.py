@@ -99,3 +99,11 @@ def test_plain_router_by_hand():
 def test_plain_sink_by_hand():
     p = plain.softmax_with_sink(np.array([[0.0, 0.0]]), 0.0)
     assert np.allclose(p, [[1 / 3, 1 / 3]])
+
+
+def test_show_command_reads_a_lefatar_folder(tmp_path, capsys):
+    from alpacca_b200.cli import main
+    d = write_random_model_dir(tmp_path / "m", copy.deepcopy(lt.TINY_Q), seed=2)
+    assert main(["show", str(d), "--tensors"]) == 0
+    out = capsys.readouterr().out
+    assert "Lefatar: 3 layers" in out and "no limit on positions" in out and "l1.mix.dkv.norm" in out
