@@ -555,12 +555,12 @@ def _moe(ff, experts, top, count, keep):
 
 DESIGN_SIZES = {
     "w1024": {"width": 1024, "layers": 8, "vocab": 32000, "dense_ff": 2816, "heads": 16, "kv_heads": 4, "head_dim": 64,
-              "mlstm": {"heads": 4, "dim": 128, "vdim": 256, "gate_cap": 15.0},
+              "mlstm": {"heads": 4, "dim": 128, "vdim": 256, "gate_cap": 12.0},
               "latent": {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "q_rank": 384, "kv_rank": 224,
                          "scale": 96 ** -0.5, "rot": {"base": 10000.0, "dims": 32}},
               "moe": _moe(704, 8, 2, 2, 1)},
     "w2048": {"width": 2048, "layers": 8, "vocab": 32000, "dense_ff": 5632, "heads": 16, "kv_heads": 4, "head_dim": 128,
-              "mlstm": {"heads": 8, "dim": 128, "vdim": 256, "gate_cap": 15.0},
+              "mlstm": {"heads": 8, "dim": 128, "vdim": 256, "gate_cap": 12.0},
               "latent": {"heads": 16, "dim": 128, "rot_dim": 32, "vdim": 128, "q_rank": 768, "kv_rank": 224,
                          "scale": 160 ** -0.5, "rot": {"base": 10000.0, "dims": 32}},
               "moe": _moe(1408, 16, 4, 4, 2)},

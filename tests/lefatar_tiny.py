@@ -48,8 +48,8 @@ TINY_P = {
 TINY_Q = {
     "architecture": "Lefatar", "vocab": 211, "width": 64, "norm": {"eps": 1e-6},
     "layers": [
-        {"type": "mlstm", "mixer": _mlstm(2, 32, 48, 15.0), "mlp": _moe(32, 8, 3, 2, 1, 2.0)},
-        {"type": "latent_attention", "mixer": _latent(4, 32, 16, 24, 48, 64, 0.15, 250000.0, 16),
+        {"type": "mlstm", "mixer": _mlstm(2, 32, 40, 11.0), "mlp": _moe(32, 8, 2, 4, 2, 1.5)},
+        {"type": "latent_attention", "mixer": _latent(4, 32, 16, 24, 48, 64, 0.15, 40000.0, 16),
          "mlp": {"kind": "dense", "ff": 96}},
         {"type": "mlstm", "mixer": _mlstm(4, 64, 20, 12.0), "mlp": {"kind": "dense", "ff": 60}},
     ],

@@ -40,8 +40,8 @@ def short(weights, prefix):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,D,V,cap", [(2, 16, 24, 8.0), (1, 24, 40, 30.0), (3, 64, 20, 15.0), (2, 128, 36, 12.0),
-                                       (2, 40, 70, 5.0), (1, 32, 33, 15.0)])
+@pytest.mark.parametrize("H,D,V,cap", [(2, 16, 24, 8.0), (1, 24, 40, 30.0), (3, 64, 20, 14.0), (2, 128, 36, 12.0),
+                                       (2, 40, 70, 5.0), (1, 32, 33, 20.0)])
 def test_matrix_memory(dtype, H, D, V, cap):
     """Two sequences side by side, fed in portions of unequal sizes down to one token; the state is carried from
     step to step.  D 16, 32, 64, 128 take the register form of the kernel, 24 and 40 the shared-memory form."""
@@ -99,7 +99,7 @@ def test_matrix_memory_state_is_zeroed_when_a_slot_is_taken_again():
 LATENT_SIZES = [  # H, D, R, V, Q, C, rotated dims, base, scale
     (3, 24, 12, 20, 40, 36, 8, 10000.0, 0.17),
     (2, 16, 8, 28, 24, 56, 8, 300.0, 0.2),
-    (5, 32, 16, 24, 48, 112, 16, 250000.0, 0.12),
+    (5, 32, 16, 24, 48, 112, 16, 70000.0, 0.12),
     (1, 8, 4, 8, 8, 8, 2, 50.0, 0.3),
     (2, 40, 24, 36, 72, 272, 24, 1000.0, 0.05),
 ]
@@ -213,7 +213,7 @@ def test_latent_attention_sink_takes_its_share():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,groups,keep,top,scale", [(8, 2, 1, 3, 2.0), (6, 3, 2, 2, 1.0), (4, 1, 1, 1, 2.5), (40, 5, 3, 7, 1.5),
+@pytest.mark.parametrize("E,groups,keep,top,scale", [(9, 3, 1, 3, 2.0), (6, 3, 2, 2, 1.0), (4, 1, 1, 1, 2.5), (40, 5, 3, 7, 1.5),
                                                       (12, 12, 4, 4, 1.0), (1, 1, 1, 1, 3.0), (64, 8, 8, 6, 1.0)])
 def test_router(dtype, E, groups, keep, top, scale):
     from alpacca_b200 import ops
@@ -229,7 +229,7 @@ def test_router(dtype, E, groups, keep, top, scale):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,groups,keep,top,ff", [(6, 3, 2, 2, 40), (4, 1, 1, 1, 24), (8, 2, 1, 3, 33)])
+@pytest.mark.parametrize("E,groups,keep,top,ff", [(6, 3, 2, 2, 40), (4, 1, 1, 1, 24), (9, 3, 1, 3, 33)])
 @pytest.mark.parametrize("T", [5, 50])
 def test_routed_experts(dtype, E, groups, keep, top, ff, T):
     """5 tokens: an expert's rows are read once for the pairs that chose it (or, for widths that are no multiple

@@ -25,7 +25,7 @@ def draw(seed):
     for _ in range(int(rng.integers(2, 6))):
         if rng.random() < 0.5:
             mixer = {"heads": pick([1, 2, 3, 4]), "dim": pick([8, 16, 24, 32, 48, 64]),
-                     "vdim": 4 * int(rng.integers(2, 19)), "gate_cap": float(pick([5.0, 8.0, 15.0, 30.0]))}
+                     "vdim": 4 * int(rng.integers(2, 19)), "gate_cap": float(pick([5.0, 8.0, 16.0, 30.0]))}
             kind = "mlstm"
         else:
             rot_dim = pick([4, 8, 12, 16])
