@@ -407,7 +407,7 @@ AB_API int ab_mlstm_step(const float* proj, int ld, int off_q, int off_k, int of
   }
   {
     // columns per CTA: few, so that a prompt of one sequence still spreads over many processors
-    const int tile = V >= 256 ? 64 : 32;
+    const int tile = (V >= 256 && (size_t)D * 64 * sizeof(float) <= 160 * 1024) ? 64 : 32;   // [D][tile] floats must fit
     dim3 grid((unsigned)n_seqs, (unsigned)H, (unsigned)((V + tile - 1) / tile));
     const bool aligned = D % 4 == 0 && (off_q % 4 == 0) && (off_k % 4 == 0) && (ld % 4 == 0);
     if (aligned && D == 16) mlstm_state_kernel<16><<<grid, tile, 0, stream>>>(a);

@@ -41,10 +41,11 @@ def short(weights, prefix):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,D,V,cap", [(2, 16, 24, 8.0), (1, 24, 40, 30.0), (3, 64, 20, 14.0), (2, 128, 36, 12.0),
-                                       (2, 40, 70, 5.0), (1, 32, 33, 20.0)])
+                                       (2, 40, 70, 5.0), (1, 32, 33, 20.0), (1, 272, 264, 10.0)])
 def test_matrix_memory(dtype, H, D, V, cap):
     """Two sequences side by side, fed in portions of unequal sizes down to one token; the state is carried from
-    step to step.  D 16, 32, 64, 128 take the register form of the kernel, 24 and 40 the shared-memory form."""
+    step to step.  D 16, 32, 64, 128 take the register form of the kernel, 24, 40 and 272 the shared-memory form
+    (272 x 64 columns: more shared memory than a kernel gets without asking)."""
     from alpacca_b200.parts import MatrixMemory
     width, eps = 56, 1e-5
     part = MatrixMemory(opts_of(dtype), width, H, D, V, cap, eps, "m")
