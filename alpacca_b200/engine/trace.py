@@ -21,9 +21,13 @@ from pathlib import Path
 
 import torch
 
+from ..cache import PAGE_SIZE
 from .engine import Engine
 from .loading import load_model_dir, resolve_dtype
 from .step import StepEntry
+
+
+MAX_LIVE = 512       # sequences that can be live at once in a replay
 
 
 def replay(model_dir, dtype, out_dir, max_tokens: int, lines, out_stream) -> int:
@@ -33,7 +37,11 @@ def replay(model_dir, dtype, out_dir, max_tokens: int, lines, out_stream) -> int
     if max_tokens <= 0:
         raise ValueError("--max-tokens must be positive")
     model = load_model_dir(model_dir, resolve_dtype(dtype), "cuda", max_positions=max_tokens)
-    engine = Engine(model, max_tokens=max_tokens, max_slots=min(max(-(-max_tokens // 64), 1), 4096))
+    # `max_tokens` counts tokens, the cache counts pages: every live sequence may leave its last page partly
+    # empty, and the live sequences may be as many as there are tokens (one token each).  So: a slot for every
+    # sequence that can be live (up to MAX_LIVE), and one page more per slot than the tokens alone need.
+    max_slots = max(1, min(max_tokens, MAX_LIVE))
+    engine = Engine(model, max_tokens=max_tokens + PAGE_SIZE * max_slots, max_slots=max_slots)
     slots: dict[str, int] = {}
     for line in lines:
         line = line.strip()
@@ -72,7 +80,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens that live requests hold at any time")
     args = ap.parse_args(argv)
     try:
         return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout)

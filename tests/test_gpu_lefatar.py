@@ -296,3 +296,23 @@ def test_run_command(dirs):
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [ln for ln in proc.stdout.splitlines() if ln.strip()]
     assert [[int(t) for t in ln.split()] for ln in lines] == [plain_greedy(name, p, 5) for p in prompts]
+
+
+def test_trace_replay_of_many_short_requests(dirs, tmp_path):
+    """Thirty requests of three tokens live at once, with --max-tokens exactly what they hold: every request has a
+    slot and a page of its own although the tokens alone would fill two pages."""
+    name = "q"
+    reqs = [some_tokens(name, 3, 200 + i) for i in range(30)]
+    steps = [{"step": 0, "entries": [{"id": f"r{i}", "tokens": r[:2], "want": [1]} for i, r in enumerate(reqs)], "end": []},
+             {"step": 1, "entries": [{"id": f"r{i}", "tokens": r[2:], "want": [0]} for i, r in enumerate(reqs)],
+              "end": [f"r{i}" for i in range(30)]}]
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(dirs[name]), "--dtype", "float32",
+                           "--out", str(out), "--max-tokens", "90"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    V = lt.CONFIGS[name]["vocab"]
+    for step, pos in ((0, 1), (1, 2)):
+        got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(-1, V)
+        want = np.stack([plain_logits(name, r)[pos] for r in reqs])
+        assert np.abs(got - want).max() < 2e-4
