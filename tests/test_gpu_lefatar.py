@@ -316,3 +316,26 @@ def test_trace_replay_of_many_short_requests(dirs, tmp_path):
         got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(-1, V)
         want = np.stack([plain_logits(name, r)[pos] for r in reqs])
         assert np.abs(got - want).max() < 2e-4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["q", "r"])
+def test_prompt_steps_replayed_from_their_graph(dirs, name, dtype):
+    """Five prompt steps of one shape (two prompts of 70 and 9 tokens on empty slots): the second is captured, the
+    later ones are replays with other tokens, slots and pages, and every one gives the plain logits."""
+    from alpacca_b200.engine.step import StepEntry
+    eng = engine_of(dirs, name, dtype)
+    held = eng.alloc_slot()          # shifts the slots of the later rounds
+    for k in range(5):
+        a, b = some_tokens(name, 70, 300 + k), some_tokens(name, 9, 320 + k)
+        if k == 3:
+            eng.free_slot(held)
+            held = None
+        sa, sb = eng.alloc_slot(), eng.alloc_slot()
+        out = eng.step([StepEntry(sa, a, list(range(70))), StepEntry(sb, b, list(range(9)))]).cpu().numpy()
+        eng.wait()
+        check(out[:70], name, a, dtype, f"lefatar {name} replayed prompt step {k}")
+        check(out[70:], name, b, dtype, f"lefatar {name} replayed prompt step {k}, second prompt")
+        eng.free_slot(sa)
+        eng.free_slot(sb)
+    assert len(eng._graphs) >= 1
