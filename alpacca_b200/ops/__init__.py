@@ -132,9 +132,10 @@ def _mark(what):
         _timeline.append((what, ev))
 
 
-def _check(rc, what):
+def _check(rc, what, kernels=1):
+    """`kernels`: how many kernels the entry point launched (some run two or three in a row)."""
     global launches
-    launches += 1
+    launches += kernels
     _mark(what)
     if rc != 0:
         if rc >= 1000:
@@ -962,7 +963,7 @@ def mlstm_step(proj, offsets, bias_i, bias_f, state, ctx, H, D, V, cap, qscale, 
         _p(proj), ld, off_q, off_k, off_v, off_g, off_i, off_f, _p(bias_i), _p(bias_f), _p(state), row, H, D, V,
         _p(ctx.cu_q), _p(ctx.slots), _p(ctx.tok_seq), B, T, ctypes.c_float(cap), ctypes.c_float(qscale), _p(coef),
         _p(o_raw), _p(norm_weight), ctypes.c_float(eps), _p(out), _dt(out), 1 if write_state else 0, _stream()),
-        "mlstm_step")
+        "mlstm_step", kernels=3)
     return out
 
 
@@ -1133,7 +1134,7 @@ def moe_route(h, router, n_tokens, groups, keep, top, scale):
     wts = torch.empty((max(n_tokens, 1), top), dtype=torch.float32, device=h.device)
     z = torch.empty((max(n_tokens, 1), E), dtype=torch.float32, device=h.device)
     _check(_lib("moe").ab_moe_route(_p(h), _dt(h), width, _p(router), n_tokens, width, E, groups, keep, top,
-                                    ctypes.c_float(scale), _p(z), _p(idx), _p(wts), _stream()), "moe_route")
+                                    ctypes.c_float(scale), _p(z), _p(idx), _p(wts), _stream()), "moe_route", kernels=2)
     return idx, wts
 
 
@@ -1165,5 +1166,6 @@ def moe_experts(h, w_up, w_down, idx, wts, out, n_tokens, activation="gelu"):
         return out
     act = torch.empty((max(n_tokens, 1) * top, ff), dtype=h.dtype, device=h.device)
     _check(_lib("moe").ab_moe_pairs(_p(h), _dt(h), width, _p(w_up), _p(w_down), _p(idx), _p(wts), _p(act), _p(out),
-                                    n_tokens, top, width, ff, E, MOE_ACTIVATIONS[activation], _stream()), "moe_experts")
+                                    n_tokens, top, width, ff, E, MOE_ACTIVATIONS[activation], _stream()), "moe_experts",
+           kernels=2)
     return out
