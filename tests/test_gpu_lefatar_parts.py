@@ -150,20 +150,24 @@ def test_latent_attention(dtype, sizes):
 
 
 @pytest.mark.parametrize("where", [0, 1, 63, 64, 127, 128, 300])
-def test_latent_attention_finds_one_far_key(where):
+@pytest.mark.parametrize("dtype,last", [("float32", 1), ("float32", 3), ("bfloat16", 1), ("bfloat16", 20)])
+def test_latent_attention_finds_one_far_key(where, dtype, last):
     """One key among 400 is made to stand out for the last query (its cached row is the query's folded form,
-    scaled): the output is that key's value, wherever it lies - the first tokens, a page's last or first row."""
+    scaled): the output is that key's row, wherever it lies - the first tokens, a page's last or first row -
+    when the query comes alone (a decode step) and when it is the last token of a portion of a prompt; in
+    32-bit (the one-warp kernel) and in bfloat16 (the tensor-core kernels)."""
+    from alpacca_b200 import ops
     sizes = (2, 16, 8, 12, 24, 40, 8, 10000.0, 0.25)
-    part, mx = latent_part("float32", sizes, 32)
-    w = short(load_part(part, seed=9, dtype="float32", std=0.3), "a")
+    part, mx = latent_part(dtype, sizes, 32)
+    w = short(load_part(part, seed=9, dtype=dtype, std=0.3), "a")
     rng = np.random.default_rng(where)
     n = 400
-    x, x64 = hidden(rng, n, 32, "float32")
-    hs = PartHarness([part.cache_spec()], "float32", max_tokens=64 * 8, max_slots=1)
+    x, x64 = hidden(rng, n, 32, dtype)
+    hs = PartHarness([part.cache_spec()], dtype, max_tokens=64 * 8, max_slots=1)
     s = hs.cache.alloc_slot()
-    ctx = hs.step([(s, n - 1)])
+    ctx = hs.step([(s, n - last)])
     view = hs.cache.entry_view(0, ctx.block_tables)
-    part.forward(x[:n - 1].contiguous(), ctx, view)
+    part.forward(x[:n - last].contiguous(), ctx, view)
     hs.done()
     # plant the key: head 0's folded query of the last token, as the plain implementation forms it
     C, R, D = mx["kv_rank"], mx["rot_dim"], mx["dim"]
@@ -173,24 +177,29 @@ def test_latent_attention_finds_one_far_key(where):
     row = np.concatenate([q_lat, np.zeros(R)])
     row = 40.0 * row / np.linalg.norm(row)
     page = int(ctx.block_tables[0][0, where // 64])
-    view.k[page, 0, where % 64] = torch.from_numpy(row).float().cuda()
-    ctx = hs.step([(s, 1)])
-    o_lat = {}
-    from alpacca_b200 import ops
-    real = ops.latent_attention
+    view.k[page, 0, where % 64] = torch.from_numpy(row).to(view.k.dtype).cuda()
+    ctx = hs.step([(s, last)])
+    seen = {}
+    names = ("latent_attention", "latent_attention_mma")
+    real = {k: getattr(ops, k) for k in names}
 
-    def spy(q_, out, *a, **k):
-        r = real(q_, out, *a, **k)
-        o_lat["o"] = out.clone()
-        return r
-    ops.latent_attention = spy
+    def spy(name):
+        def call(q_, out, *a, **k):
+            r = real[name](q_, out, *a, **k)
+            seen["o"] = out.float().clone()
+            return r
+        return call
+    for k in names:
+        setattr(ops, k, spy(k))
     try:
-        part.forward(x[n - 1:].contiguous(), ctx, hs.cache.entry_view(0, ctx.block_tables))
+        part.forward(x[n - last:].contiguous(), ctx, hs.cache.entry_view(0, ctx.block_tables))
     finally:
-        ops.latent_attention = real
+        for k in names:
+            setattr(ops, k, real[k])
     hs.done()
-    head0 = o_lat["o"][0, :C].cpu().numpy()
-    assert np.abs(head0 - row[:C]).max() < 1e-3 * np.abs(row).max(), "the planted key's row is not what head 0 returns"
+    head0 = seen["o"][last - 1, :C].cpu().numpy()        # the last token's first head: its weighted sum of c
+    tol = 1e-3 if dtype == "float32" else 2e-2
+    assert np.abs(head0 - row[:C]).max() < tol * np.abs(row).max(), "the planted key's row is not what head 0 returns"
 
 
 def test_latent_attention_sink_takes_its_share():
