@@ -32,7 +32,9 @@ PAGE_SIZE = 64
 class KVLayerView:
     """What an attention mixer gets: its entry's pages and the step's block table."""
     k: torch.Tensor            # [n_pages, K, PAGE_SIZE, D]
-    v: torch.Tensor | None     # None for a group that keeps one row per token only (`KVSpec.values` off)
+    v: torch.Tensor | None     # the same shape, or [n_pages, value heads, PAGE_SIZE, value size] where the spec
+                               # gives the values sizes of their own; None for a group that keeps one row per
+                               # token only (`KVSpec.values` off)
     block_table: torch.Tensor  # int32 [B, W]: page of position p of batch row b at [b, p // PAGE_SIZE]
     group: "KVGroup"
 
@@ -49,14 +51,17 @@ class KVGroup:
         self.spec, self.n_entries, self.n_pages = spec, n_entries, int(n_pages)
         shape = (n_entries, self.n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if spec.values else None
+        v_shape = (n_entries, self.n_pages, spec.v_heads, PAGE_SIZE, spec.v_dim)
+        self.v = torch.zeros(v_shape, dtype=dtype, device=device) if spec.values else None
         self.pages = IdPool(self.n_pages, "cache page")
         self.page_lists: dict[int, list[int]] = {}   # slot -> page of each page index (-1: given back)
 
     @property
     def bytes_per_token(self) -> int:
-        return ((2 if self.spec.values else 1) * self.n_entries * self.spec.n_kv_heads * self.spec.head_dim
-                * self.k.element_size())
+        per_entry = self.spec.n_kv_heads * self.spec.head_dim
+        if self.spec.values:
+            per_entry += self.spec.v_heads * self.spec.v_dim
+        return self.n_entries * per_entry * self.k.element_size()
 
     def open(self, slot: int) -> None:
         self.page_lists[slot] = []
@@ -258,7 +263,7 @@ class SequenceCache:
             assert set(g.page_lists) == set(self.lengths)
 
     def describe(self) -> str:
-        kv = sum(g.k.numel() * g.k.element_size() * (2 if g.v is not None else 1) for g in self.kv_groups)
+        kv = sum((g.k.numel() + (g.v.numel() if g.v is not None else 0)) * g.k.element_size() for g in self.kv_groups)
         st = sum(g.state.numel() * g.state.element_size() for g in self.state_groups)
         return (f"cache: {self.n_pages} pages of {PAGE_SIZE} tokens in {len(self.kv_groups)} key/value group(s) "
                 f"({kv / 2**20:.1f} MiB), {len(self.state_groups)} state group(s) ({st / 2**20:.1f} MiB), "

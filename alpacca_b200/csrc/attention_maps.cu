@@ -1,0 +1,254 @@
+// Grouped-query attention over the paged cache whose keys and values have sizes and head counts of their
+// own, with one or several score maps per head, 32-bit arithmetic.  Two kernels:
+//
+//   prepare   one warp per (token, vector): a query vector is (optionally) divided by its root mean square and
+//             multiplied by a weight, then rotated by position, in place; a key vector likewise, and written to
+//             the key pages; a value vector is copied to the value pages as it was projected.  The values may be
+//             read from the same place as the keys (values that are the keys before norm and rotation).
+//   attend    one warp per (token, head).  A head has M maps; map m of head h has the query vector h*M + m
+//             and reads key head (h / (H/G)) * M + m and value head h / (H/G):
+//               a_m = softmax_s((q_m . k_m,s) * scale) v_s   over lo <= s <= p, lo = max(0, p - window + 1)
+//             (window 0: all), with exp(sink_h) as one more term of the denominator when sinks are given;
+//               o = a_0 + sum_{m>0} coef * a_m,
+//             then, if asked, o is divided by its root mean square (eps inside the root), and multiplied by
+//             out_scale.  The softmax is the running form, in key order; nothing is shared between warps, so
+//             a token's result does not depend on the rest of the batch.
+//
+// Key pages [n_pages, G*M, page, Dk], value pages [n_pages, G, page, Dv]; one block table for both.
+// Rotation: the first n_rot dims of a vector, pairing 0 = (2i, 2i+1), 1 = (i, i + n_rot/2); tables
+// float32 [positions, n_rot/2].  (u, v) -> (u cos - v sin, v cos + u sin).
+#include "common.cuh"
+#include "launch.cuh"
+
+#define AM_MAX_DIM 256
+
+struct PrepareArgs {
+  void* buf;               // [T, stride] projected rows; query vectors are rewritten in place
+  int stride, off_q, off_k, off_v;
+  int n_q, n_k, n_v;       // vectors per token: H*M queries, G*M keys, G values
+  int Dk, Dv;
+  const float* q_weight;   // [Dk] or null: no norm
+  const float* k_weight;
+  float eps;
+  const float* cos_t; const float* sin_t; int n_rot, pairing;
+  const int* tok_pos; const int* tok_seq;
+  const int* block_table; int table_width;
+  void* k_pages; void* v_pages; int page_size;
+  int n_tokens, write_cache;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_prepare_kernel(PrepareArgs a) {
+  __shared__ float stage[4][AM_MAX_DIM];
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int per_tok = a.n_q + a.n_k + a.n_v;
+  const long long w = (long long)blockIdx.x * 4 + wib;
+  if (w >= (long long)a.n_tokens * per_tok) return;
+  const int t = (int)(w / per_tok), vec = (int)(w - (long long)t * per_tok);
+  const int b = a.tok_seq[t];
+  if (b < 0) return;
+  const int pos = a.tok_pos[t];
+  T* row = reinterpret_cast<T*>(a.buf) + (size_t)t * a.stride;
+  const int page = a.write_cache ? a.block_table[(size_t)b * a.table_width + pos / a.page_size] : 0;
+  const int in_page = pos % a.page_size;
+  if (vec >= a.n_q + a.n_k) {                       // a value vector: copied as projected
+    if (!a.write_cache) return;
+    const int g = vec - a.n_q - a.n_k;
+    const T* src = row + a.off_v + (size_t)g * a.Dv;
+    T* dst = reinterpret_cast<T*>(a.v_pages) + (((size_t)page * a.n_v + g) * a.page_size + in_page) * a.Dv;
+    for (int d = lane; d < a.Dv; d += 32) dst[d] = src[d];
+    return;
+  }
+  const bool is_q = vec < a.n_q;
+  if (!is_q && !a.write_cache) return;
+  const int head = is_q ? vec : vec - a.n_q;
+  const int D = a.Dk;
+  T* src = row + (is_q ? a.off_q : a.off_k) + (size_t)head * D;
+  const float* weight = is_q ? a.q_weight : a.k_weight;
+  float* x = stage[wib];
+  float ss = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float v = to_f32(src[d]);
+    x[d] = v;
+    ss += v * v;
+  }
+  if (weight != nullptr) {
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+    for (int d = lane; d < D; d += 32) x[d] = x[d] * inv * weight[d];
+  }
+  __syncwarp();
+  T* dst = is_q ? src
+                : reinterpret_cast<T*>(a.k_pages) + (((size_t)page * a.n_k + head) * a.page_size + in_page) * D;
+  const int half = a.n_rot >> 1;
+  const float* cr = a.cos_t ? a.cos_t + (size_t)pos * half : nullptr;
+  const float* sr = a.cos_t ? a.sin_t + (size_t)pos * half : nullptr;
+  for (int d = lane; d < D; d += 32) {
+    float v = x[d];
+    if (cr != nullptr && d < a.n_rot) {
+      int i, partner;
+      bool first;
+      if (a.pairing == 0) { i = d >> 1; first = (d & 1) == 0; partner = d ^ 1; }
+      else { first = d < half; i = first ? d : d - half; partner = first ? d + half : d - half; }
+      const float p = x[partner], c = cr[i], s = sr[i];
+      v = first ? v * c - p * s : v * c + p * s;
+    }
+    dst[d] = from_f32<T>(v);
+  }
+}
+
+struct AttendArgs {
+  const void* q; int q_stride;      // query vectors of token t at q + t*q_stride + (h*M + m)*Dk
+  void* out;                        // [T, H*Dv]
+  const void* k_pages; const void* v_pages;
+  const int* block_table; int table_width;
+  const int* tok_pos; const int* tok_seq;
+  int n_tokens, H, G, M, Dk, Dv, page_size;
+  float scale; int window;
+  const float* sink;                // [H] or null
+  float coef;                       // weight of every map after the first
+  int unit_norm; float eps, out_scale;
+};
+
+template <typename T, int KPL, int VPL>
+__global__ void __launch_bounds__(128)
+attention_maps_kernel(AttendArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)a.n_tokens * a.H) return;
+  const int t = (int)(w / a.H), h = (int)(w - (long long)t * a.H);
+  const int Dk = a.Dk, Dv = a.Dv, M = a.M;
+  T* o = reinterpret_cast<T*>(a.out) + ((size_t)t * a.H + h) * Dv;
+  const int b = a.tok_seq[t];
+  if (b < 0) {
+    for (int d = lane; d < Dv; d += 32) o[d] = from_f32<T>(0.f);
+    return;
+  }
+  const int pos = a.tok_pos[t];
+  const int g = h / (a.H / a.G);
+  const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  const int* bt = a.block_table + (size_t)b * a.table_width;
+  const T* kp = reinterpret_cast<const T*>(a.k_pages);
+  const T* vp = reinterpret_cast<const T*>(a.v_pages);
+  float total[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) total[j] = 0.f;
+  for (int m = 0; m < M; ++m) {
+    const T* qv = reinterpret_cast<const T*>(a.q) + (size_t)t * a.q_stride + (size_t)(h * M + m) * Dk;
+    const int kh = g * M + m;
+    float qr[KPL], acc[VPL];
+#pragma unroll
+    for (int j = 0; j < KPL; ++j) {
+      const int d = lane + 32 * j;
+      qr[j] = d < Dk ? to_f32(qv[d]) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) acc[j] = 0.f;
+    float mx = -INFINITY, l = 0.f;
+    for (int s = lo; s <= pos; ++s) {
+      const int page = bt[s / a.page_size], in_page = s % a.page_size;
+      const T* kv = kp + (((size_t)page * (a.G * M) + kh) * a.page_size + in_page) * Dk;
+      const T* vv = vp + (((size_t)page * a.G + g) * a.page_size + in_page) * Dv;
+      float part = 0.f;
+#pragma unroll
+      for (int j = 0; j < KPL; ++j) {
+        const int d = lane + 32 * j;
+        if (d < Dk) part += qr[j] * to_f32(kv[d]);
+      }
+      const float score = warp_sum(part) * a.scale;
+      const float m_new = fmaxf(mx, score);
+      const float corr = expf(mx - m_new);   // exp(-inf) = 0 on the first key
+      const float p = expf(score - m_new);
+      l = l * corr + p;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int d = lane + 32 * j;
+        if (d < Dv) acc[j] = acc[j] * corr + p * to_f32(vv[d]);
+      }
+      mx = m_new;
+    }
+    if (a.sink != nullptr) {
+      // the sink has no key and no value: it only joins the denominator
+      const float sk = a.sink[h];
+      const float m_new = fmaxf(mx, sk);
+      const float corr = expf(mx - m_new);
+      l = l * corr + expf(sk - m_new);
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) acc[j] *= corr;
+    }
+    const float wgt = (m == 0 ? 1.0f : a.coef) / l;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) total[j] += acc[j] * wgt;
+  }
+  float mul = a.out_scale;
+  if (a.unit_norm) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) ss += total[j] * total[j];   // lanes past Dv hold zeros
+    ss = warp_sum(ss);
+    mul *= 1.0f / sqrtf(ss / (float)Dv + a.eps);
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int d = lane + 32 * j;
+    if (d < Dv) o[d] = from_f32<T>(total[j] * mul);
+  }
+}
+
+AB_API int ab_attention_prepare(void* buf, int dtype, int stride, int off_q, int off_k, int off_v, int n_q, int n_k,
+                                int n_v, int Dk, int Dv, const float* q_weight, const float* k_weight, float eps,
+                                const float* cos_t, const float* sin_t, int n_rot, int pairing, const int* tok_pos,
+                                const int* tok_seq, const int* block_table, int table_width, void* k_pages,
+                                void* v_pages, int page_size, int n_tokens, int write_cache, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (Dk <= 0 || Dk > AM_MAX_DIM || Dv <= 0 || n_q < 0 || n_k < 0 || n_v < 0 || page_size <= 0) return AB_BAD_ARG;
+  if (n_rot < 0 || n_rot > Dk || (n_rot & 1) || pairing < 0 || pairing > 1) return AB_BAD_ARG;
+  if (!cos_t || !sin_t || n_rot == 0) { cos_t = sin_t = nullptr; n_rot = 0; }
+  PrepareArgs a{buf, stride, off_q, off_k, off_v, n_q, n_k, n_v, Dk, Dv, q_weight, k_weight, eps, cos_t, sin_t, n_rot,
+                pairing, tok_pos, tok_seq, block_table, table_width, k_pages, v_pages, page_size, n_tokens, write_cache};
+  const long long warps = (long long)n_tokens * (n_q + n_k + n_v);
+  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  if (dtype == AB_F32) ab_launch(attention_prepare_kernel<float>, dim3(blocks), dim3(128), 0, stream, a);
+  else if (dtype == AB_BF16) ab_launch(attention_prepare_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, a);
+  else return AB_BAD_ARG;
+  return ab_launch_status();
+}
+
+template <typename T>
+static int launch_attend(const AttendArgs& a, cudaStream_t stream) {
+  const long long warps = (long long)a.n_tokens * a.H;
+  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  const int kc = a.Dk <= 64 ? 2 : (a.Dk <= 128 ? 4 : 8), vc = a.Dv <= 64 ? 2 : (a.Dv <= 128 ? 4 : 8);
+#define AB_GO(KPL, VPL) ab_launch(attention_maps_kernel<T, KPL, VPL>, dim3(blocks), dim3(128), 0, stream, a)
+  if (kc == 2 && vc == 2) AB_GO(2, 2);
+  else if (kc == 2 && vc == 4) AB_GO(2, 4);
+  else if (kc == 2) AB_GO(2, 8);
+  else if (kc == 4 && vc == 2) AB_GO(4, 2);
+  else if (kc == 4 && vc == 4) AB_GO(4, 4);
+  else if (kc == 4) AB_GO(4, 8);
+  else if (vc == 2) AB_GO(8, 2);
+  else if (vc == 4) AB_GO(8, 4);
+  else AB_GO(8, 8);
+#undef AB_GO
+  return ab_launch_status();
+}
+
+AB_API int ab_attention_maps(const void* q, int q_stride, void* out, int dtype, const void* k_pages,
+                             const void* v_pages, const int* block_table, int table_width, const int* tok_pos,
+                             const int* tok_seq, int n_tokens, int H, int G, int M, int Dk, int Dv, int page_size,
+                             float scale, int window, const float* sink, float coef, int unit_norm, float eps,
+                             float out_scale, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (Dk <= 0 || Dk > AM_MAX_DIM || Dv <= 0 || Dv > AM_MAX_DIM || H <= 0 || G <= 0 || H % G || M <= 0 || page_size <= 0)
+    return AB_BAD_ARG;
+  AttendArgs a{q, q_stride, out, k_pages, v_pages, block_table, table_width, tok_pos, tok_seq, n_tokens, H, G, M, Dk,
+               Dv, page_size, scale, window, sink, coef, unit_norm, eps, out_scale};
+  if (dtype == AB_F32) return launch_attend<float>(a, stream);
+  if (dtype == AB_BF16) return launch_attend<bf16>(a, stream);
+  return AB_BAD_ARG;
+}

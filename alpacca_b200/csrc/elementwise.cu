@@ -510,7 +510,15 @@ AB_API int ab_rope_append(void* qkv, int dtype, const float* cos_t, const float*
 // 16*q + r hold gate 8*q + r, columns 16*q + 8 + r hold up 8*q + r (r < 8), which
 // is the order in which the skinny-matrix kernel's accumulators meet them.
 // ---------------------------------------------------------------------------
-template <typename T>
+// ACT: 0 = SiLU g / (1 + exp(-g)), 1 = ReLU max(g, 0), 2 = GELU in its tanh form
+template <int ACT>
+__device__ __forceinline__ float gate_act(float g) {
+  if (ACT == 1) return fmaxf(g, 0.f);
+  if (ACT == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
+template <typename T, int ACT>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, size_t total, int F) {
   pdl_wait();
   pdl_trigger();
@@ -522,10 +530,11 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, siz
   const int q = j >> 3, r = j & 7;
   const float g = to_f32(row[16 * q + r]);
   const float u = to_f32(row[16 * q + 8 + r]);
-  act[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  act[idx] = from_f32<T>(gate_act<ACT>(g) * u);
 }
 
 // bfloat16, 8 outputs per thread: one 16-byte piece of gate, one of up, one of output
+template <int ACT>
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ act, size_t n_units, int units_per_row) {
   pdl_wait();
   pdl_trigger();
@@ -542,30 +551,41 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
   for (int i = 0; i < 4; ++i) {
     const float g0 = __uint_as_float(gw[i] << 16), g1 = __uint_as_float(gw[i] & 0xffff0000u);
     const float u0 = __uint_as_float(uw[i] << 16), u1 = __uint_as_float(uw[i] & 0xffff0000u);
-    __nv_bfloat162 r = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+    __nv_bfloat162 r = __floats2bfloat162_rn(gate_act<ACT>(g0) * u0, gate_act<ACT>(g1) * u1);
     ow[i] = *reinterpret_cast<uint32_t*>(&r);
   }
   *reinterpret_cast<uint4*>(act + u * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
 }
 
-AB_API int ab_swiglu(const void* gu, void* act, int dtype, int n_rows, int F, cudaStream_t stream) {
+template <int ACT>
+static int gated_act_launch(const void* gu, void* act, int dtype, int n_rows, int F, cudaStream_t stream) {
   size_t total = (size_t)n_rows * F;
   if (total == 0) return AB_OK;
   if (F % 8) return AB_BAD_ARG;
   if (dtype == AB_BF16) {
     const size_t n_units = total / 8;
-    ab_launch(swiglu_bf16x8_kernel, (unsigned)((n_units + 255) / 256), 256, 0, stream, (const bf16*)gu, (bf16*)act,
+    ab_launch(swiglu_bf16x8_kernel<ACT>, (unsigned)((n_units + 255) / 256), 256, 0, stream, (const bf16*)gu, (bf16*)act,
               n_units, F / 8);
     return ab_launch_status();
   }
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == AB_F32)
-    ab_launch(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)act, total, F);
-  else if (dtype == AB_BF16)
-    ab_launch(swiglu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, (bf16*)act, total, F);
+    ab_launch(swiglu_kernel<float, ACT>, blocks, 256, 0, stream, (const float*)gu, (float*)act, total, F);
   else
     return AB_BAD_ARG;
   return ab_launch_status();
+}
+
+AB_API int ab_swiglu(const void* gu, void* act, int dtype, int n_rows, int F, cudaStream_t stream) {
+  return gated_act_launch<0>(gu, act, dtype, n_rows, F, stream);
+}
+
+// The same with another activation on the gate (`kind` as ACT above).
+AB_API int ab_gated_act(const void* gu, void* act, int dtype, int n_rows, int F, int kind, cudaStream_t stream) {
+  if (kind == 0) return gated_act_launch<0>(gu, act, dtype, n_rows, F, stream);
+  if (kind == 1) return gated_act_launch<1>(gu, act, dtype, n_rows, F, stream);
+  if (kind == 2) return gated_act_launch<2>(gu, act, dtype, n_rows, F, stream);
+  return AB_BAD_ARG;
 }
 
 // ---------------------------------------------------------------------------

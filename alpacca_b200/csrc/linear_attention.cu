@@ -1,0 +1,173 @@
+// Linear attention with a fixed decay per head over packed sequences ("lightning attention").
+//
+// Per head, with q_t = silu(zq_t), k_t = silu(zk_t) (D dims), v_t = silu(zv_t) (V dims), a decay 0 < a <= 1 that
+// the head keeps for good, and S_0 = 0:
+//   S_t = a S_{t-1} + k_t v_t^T        [D, V]
+//   o_t = S_t^T q_t
+// The heads of a token are then divided by their common root mean square (all H*V values together), multiplied
+// by a weight and by sigmoid(g_t).  The state, the decay and every sum are 32-bit.
+//
+// Two forms of the walk over the tokens share one entry point and give the same sums up to rounding:
+//   walk     one CTA per (sequence, head, 32 columns of S): a column's D entries are spread over the registers
+//            of 4 threads (4 warps, each holding a quarter of the rows for 32 columns); q and k of 8 tokens at
+//            a time are brought to shared memory with the activation applied; a thread leaves its share of
+//            S^T q in shared memory, and the four shares are added in a fixed order after the batch's last token;
+//   chunks   (prompts) see the second half of this file.
+// The state of a sequence is read when the step starts and written back when it ends, so a prompt may be cut
+// anywhere and a decode step is the same code with one token.  The projections come as one float32 row per
+// token: zq | zk | zv | g at given offsets.
+#include "common.cuh"
+#include "launch.cuh"
+
+struct LinAttnArgs {
+  const float* proj;       // [T, ld]
+  int ld, off_q, off_k, off_v, off_g;
+  const float* decay;      // [H]
+  float* state;            // [slots, H, D, V]
+  int H, D, V;
+  const int* cu_q;         // [B + 1]
+  const int* slots;        // [B]
+  const int* tok_seq;      // [T], -1: a row without a sequence
+  float* o_raw;            // [T, H, V]
+  int write_state;
+};
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+#define LA_COLS 32
+#define LA_SLICES 4
+#define LA_TB 8
+
+// DPT: rows of S per thread (a multiple of 4); the four slices cover 4 * DPT >= D rows
+template <int DPT>
+__global__ void __launch_bounds__(LA_COLS * LA_SLICES)
+linattn_walk_kernel(LinAttnArgs a) {
+  constexpr int DP = DPT * LA_SLICES;
+  __shared__ __align__(16) float qs[LA_TB][DP];
+  __shared__ __align__(16) float ks[LA_TB][DP];
+  __shared__ float vs[LA_TB][LA_COLS];
+  __shared__ float part[LA_TB][LA_SLICES][LA_COLS];
+  pdl_wait();
+  pdl_trigger();
+  const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * LA_COLS;
+  const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
+  const int slot = a.slots[b];
+  if (slot < 0 || t1 <= t0 || a.tok_seq[t0] < 0) return;
+  const int tid = threadIdx.x, c = tid & 31, r = tid >> 5;
+  const int D = a.D, V = a.V, col = c0 + c;
+  const float lam = a.decay[h];
+  float* st = a.state + ((size_t)slot * a.H + h) * (size_t)D * V;
+  float s[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = r * DPT + i;
+    s[i] = (d < D && col < V) ? st[(size_t)d * V + col] : 0.f;
+  }
+  for (int tb = t0; tb < t1; tb += LA_TB) {
+    const int n = min(LA_TB, t1 - tb);
+    for (int i = tid; i < n * DP; i += LA_COLS * LA_SLICES) {
+      const int tok = i / DP, d = i - tok * DP;
+      const float* row = a.proj + (size_t)(tb + tok) * a.ld;
+      qs[tok][d] = d < D ? silu_f(row[a.off_q + h * D + d]) : 0.f;
+      ks[tok][d] = d < D ? silu_f(row[a.off_k + h * D + d]) : 0.f;
+    }
+    for (int i = tid; i < n * LA_COLS; i += LA_COLS * LA_SLICES) {
+      const int tok = i / LA_COLS, cc = i - tok * LA_COLS;
+      vs[tok][cc] = (c0 + cc < V) ? silu_f(a.proj[(size_t)(tb + tok) * a.ld + a.off_v + h * V + c0 + cc]) : 0.f;
+    }
+    __syncthreads();
+    for (int tok = 0; tok < n; ++tok) {
+      const float vv = vs[tok][c];
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[tok][r * DPT + i]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[tok][r * DPT + i]);
+        s[i] = fmaf(lam, s[i], k4.x * vv);
+        acc0 = fmaf(s[i], q4.x, acc0);
+        s[i + 1] = fmaf(lam, s[i + 1], k4.y * vv);
+        acc1 = fmaf(s[i + 1], q4.y, acc1);
+        s[i + 2] = fmaf(lam, s[i + 2], k4.z * vv);
+        acc0 = fmaf(s[i + 2], q4.z, acc0);
+        s[i + 3] = fmaf(lam, s[i + 3], k4.w * vv);
+        acc1 = fmaf(s[i + 3], q4.w, acc1);
+      }
+      part[tok][r][c] = acc0 + acc1;
+    }
+    __syncthreads();
+    for (int i = tid; i < n * LA_COLS; i += LA_COLS * LA_SLICES) {
+      const int tok = i / LA_COLS, cc = i - tok * LA_COLS;
+      if (c0 + cc < V)
+        a.o_raw[((size_t)(tb + tok) * a.H + h) * V + c0 + cc] =
+            ((part[tok][0][cc] + part[tok][1][cc]) + part[tok][2][cc]) + part[tok][3][cc];
+    }
+    __syncthreads();
+  }
+  if (a.write_state && col < V) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = r * DPT + i;
+      if (d < D) st[(size_t)d * V + col] = s[i];
+    }
+  }
+}
+
+// out[t, j] = o[t, j] / rms(o[t, :]) * weight[j] * sigmoid(g[t, j]) over all H*V values of a token; a block per token
+template <typename T>
+__global__ void linattn_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, int ld, int off_g,
+                                      const float* __restrict__ weight, const int* __restrict__ tok_seq,
+                                      T* __restrict__ out, int n, float eps) {
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  T* y = out + (size_t)t * n;
+  if (tok_seq[t] < 0) {
+    for (int j = threadIdx.x; j < n; j += blockDim.x) y[j] = from_f32<T>(0.f);
+    return;
+  }
+  const float* o = o_raw + (size_t)t * n;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) ss += o[j] * o[j];
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  const float* g = proj + (size_t)t * ld + off_g;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float gate = 1.0f / (1.0f + expf(-g[j]));
+    y[j] = from_f32<T>(o[j] * inv * weight[j] * gate);
+  }
+}
+
+AB_API int ab_linear_attention_max_dim() { return 64 * LA_SLICES; }
+
+AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int off_k, int off_v, int off_g,
+                                    const float* decay, float* state, int H, int D, int V, const int* cu_q,
+                                    const int* slots, const int* tok_seq, int n_seqs, int n_tokens, float* o_raw,
+                                    const float* weight, float eps, void* out, int out_dtype, int write_state,
+                                    cudaStream_t stream) {
+  if (n_seqs <= 0 || n_tokens <= 0) return AB_OK;
+  if (H <= 0 || D <= 0 || V <= 0 || D > 64 * LA_SLICES || H > 65535) return AB_BAD_ARG;
+  LinAttnArgs a{proj, ld, off_q, off_k, off_v, off_g, decay, state, H, D, V, cu_q, slots, tok_seq, o_raw, write_state};
+  const unsigned col_tiles = (unsigned)((V + LA_COLS - 1) / LA_COLS);
+  if (col_tiles > 65535) return AB_BAD_ARG;
+  dim3 grid((unsigned)n_seqs, (unsigned)H, col_tiles), block(LA_COLS * LA_SLICES);
+  const int dpt = (D + LA_SLICES - 1) / LA_SLICES;
+  if (dpt <= 4) ab_launch(linattn_walk_kernel<4>, grid, block, 0, stream, a);
+  else if (dpt <= 8) ab_launch(linattn_walk_kernel<8>, grid, block, 0, stream, a);
+  else if (dpt <= 16) ab_launch(linattn_walk_kernel<16>, grid, block, 0, stream, a);
+  else if (dpt <= 32) ab_launch(linattn_walk_kernel<32>, grid, block, 0, stream, a);
+  else ab_launch(linattn_walk_kernel<64>, grid, block, 0, stream, a);
+  int rc = ab_launch_status();
+  if (rc) return rc;
+  const int n = H * V;
+  const int threads = n >= 1024 ? 256 : 128;
+  if (out_dtype == AB_F32)
+    ab_launch(linattn_output_kernel<float>, dim3((unsigned)n_tokens), dim3(threads), 0, stream, (const float*)o_raw, proj,
+              ld, off_g, weight, tok_seq, (float*)out, n, eps);
+  else if (out_dtype == AB_BF16)
+    ab_launch(linattn_output_kernel<bf16>, dim3((unsigned)n_tokens), dim3(threads), 0, stream, (const float*)o_raw, proj,
+              ld, off_g, weight, tok_seq, (bf16*)out, n, eps);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
+}

@@ -7,7 +7,9 @@ entries it uses.  Naming a layer in two runs executes it twice (each run with
 cache entries of its own); a run whose `reads_entry_of` names an earlier run
 reads that run's cache and writes none.  What a run keeps is the block's to say
 (`cache_specs()`): one entry for each of its parts that keeps keys and values or
-a state, none for a block that keeps nothing.
+a state, none for a block that keeps nothing.  A run may also name a part that acts on the stream right before
+it (`enter`: one of the spec's `stream_parts` and the argument it is called with, e.g. the learned offset
+of a loop's pass).
 
 `DecoderModel` executes a spec for one step: embed the step's tokens, run the
 schedule, norm the wanted rows, project them to logits
@@ -29,6 +31,8 @@ from ..weights.loader import Fetcher, check_names
 class Run:
     layer: int                       # index into DecoderSpec.layers
     reads_entry_of: int | None = None  # index of an earlier run whose cache this run reads
+    enter: tuple | None = None         # (index into DecoderSpec.stream_parts, argument): called as
+                                       # part.forward(stream, ctx, argument) right before the run
 
 
 @dataclass
@@ -39,6 +43,8 @@ class DecoderSpec:
     head: VocabHead
     schedule: list[Run] = field(default_factory=list)
     position: PositionEncoding | None = None   # an encoding that adds to the embeddings, if any
+    stream_parts: list = field(default_factory=list)   # parts with weights that no layer owns alone: what runs
+                                                       # name in `enter`, tables that several layers read
     stop_token_ids: tuple = ()
     vocab_size: int = 0
 
@@ -51,6 +57,9 @@ class DecoderSpec:
             if r.reads_entry_of is not None:
                 if not 0 <= r.reads_entry_of < i or self.schedule[r.reads_entry_of].reads_entry_of is not None:
                     raise ValueError(f"run {i} must read the cache of an earlier run that owns one")
+            if r.enter is not None and not 0 <= r.enter[0] < len(self.stream_parts):
+                raise ValueError(f"run {i} enters through stream part {r.enter[0]}, the model has "
+                                 f"{len(self.stream_parts)}")
         if not self.vocab_size:
             self.vocab_size = self.head.vocab
 
@@ -77,7 +86,7 @@ class DecoderModel(Part):
 
     def children(self):
         s = self.spec
-        out = [s.embedding, *s.layers, s.final_norm, s.head]
+        out = [s.embedding, *s.stream_parts, *s.layers, s.final_norm, s.head]
         if s.position is not None:
             out.append(s.position)
         return out
@@ -116,6 +125,8 @@ class DecoderModel(Part):
         if every row's logits are wanted, in order)."""
         s = self.spec
         if i + 1 < len(s.schedule):
+            if s.schedule[i + 1].enter is not None:      # something is added to the stream in between
+                return None
             first = getattr(s.layers[s.schedule[i + 1].layer], "first_norm", None)
             return first(ctx.n_tokens) if first is not None else None
         accepts = getattr(s.head, "accepts_owed_norm", None)
@@ -132,6 +143,8 @@ class DecoderModel(Part):
             s.position.add_to_embeddings(stream.residual, ctx)
         for i, run in enumerate(s.schedule):
             view = self._views(i, cache, ctx.block_tables)
+            if run.enter is not None:
+                s.stream_parts[run.enter[0]].forward(stream, ctx, run.enter[1])
             stream.next_norm = self._reader_after(i, ctx)
             s.layers[run.layer].forward(stream, ctx, view, write_cache=run.reads_entry_of is None)
         stream.next_norm = None

@@ -1169,3 +1169,245 @@ def moe_experts(h, w_up, w_down, idx, wts, out, n_tokens, activation="gelu"):
                                     n_tokens, top, width, ff, E, MOE_ACTIVATIONS[activation], _stream()), "moe_experts",
            kernels=2)
     return out
+
+
+# ---------------------------------------------------------------------------
+# gated feed-forwards with other activations, linear attention with a fixed decay, attention with several score
+# maps and values of their own size, small kernels on the residual stream
+
+GATE_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def gated_act(gu, out, activation="silu", n_rows=None):
+    """out[t,j] = act(gate) * up from the fused, 8-row interleaved product gu [T,2F] (`swiglu` with a choice of
+    activation: "silu", "relu", "gelu_tanh")."""
+    _cuda(gu, out)
+    _need(activation in GATE_ACTIVATIONS, f"gated_act: activation {activation!r} is not one of {tuple(GATE_ACTIVATIONS)}")
+    F = gu.shape[-1] // 2
+    n = gu.numel() // (2 * F) if n_rows is None else n_rows
+    _need(gu.is_contiguous() and out.is_contiguous() and out.dtype == gu.dtype and out.shape[-1] == F
+          and out.numel() >= n * F and gu.numel() >= n * 2 * F, "gated_act: gu [T,2F], out [T,F], same dtype")
+    _need(F % 8 == 0, f"gated_act: the feed-forward width {F} must be a multiple of 8")
+    _check(_lib("elementwise").ab_gated_act(_p(gu), _p(out), _dt(gu), n, F, GATE_ACTIVATIONS[activation], _stream()),
+           "gated_act")
+    return out
+
+
+def linear_attention_max_dim() -> int:
+    """The largest query/key size per head that `linear_attention_step` takes."""
+    return 256
+
+
+def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight, eps, out, write_state=True):
+    """Linear attention with a fixed decay per head over the step's tokens, from each sequence's state to its
+    new state (csrc/linear_attention.cu).
+
+    proj float32 [T, N]: one row per token with zq | zk | zv | g at `offsets` (four column offsets, before the
+    activation); decay float32 [H]; state float32 [slots, H, D, V]; out [T, H*V] of the activation dtype gets
+    o / rms(o over all heads) * norm_weight * sigmoid(g)."""
+    _cuda(proj, decay, state, norm_weight, out)
+    T, B = ctx.n_tokens, ctx.n_seqs
+    off_q, off_k, off_v, off_g = (int(o) for o in offsets)
+    ld = proj.shape[-1]
+    _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.numel() >= T * ld,
+          "linear_attention_step: proj must be contiguous float32 [T, N]")
+    _need(min(off_q, off_k, off_v, off_g) >= 0
+          and max(off_q + H * D, off_k + H * D, off_v + H * V, off_g + H * V) <= ld,
+          "linear_attention_step: an offset reaches beyond the projected row")
+    _need(0 < D <= linear_attention_max_dim(), f"linear_attention_step: {D} dims per head are outside 1..256")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, D, V),
+          f"linear_attention_step: state must be contiguous float32 [slots, {H}, {D}, {V}]")
+    _need(decay.dtype == torch.float32 and decay.numel() == H and decay.is_contiguous(),
+          "linear_attention_step: decay float32 [H]")
+    _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == H * V and norm_weight.is_contiguous(),
+          "linear_attention_step: norm weight float32 [H*V]")
+    _need(out.is_contiguous() and out.shape[-1] == H * V and out.numel() >= T * H * V,
+          "linear_attention_step: out [T, H*V]")
+    _i32(ctx.cu_q, B + 1, "cu_q")
+    _i32(ctx.slots, B, "slots")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    o_raw = torch.empty((T, H * V), dtype=torch.float32, device=proj.device)
+    _check(_lib("linear_attention").ab_linear_attention_step(
+        _p(proj), ld, off_q, off_k, off_v, off_g, _p(decay), _p(state), H, D, V, _p(ctx.cu_q), _p(ctx.slots),
+        _p(ctx.tok_seq), B, T, _p(o_raw), _p(norm_weight), ctypes.c_float(eps), _p(out), _dt(out),
+        1 if write_state else 0, _stream()), "linear_attention_step", kernels=2)
+    return out
+
+
+ATTENTION_MAPS_MAX_DIM = 256
+
+
+def attention_prepare(buf, offsets, H, G, M, Dk, Dv, cache, ctx, q_weight=None, k_weight=None, eps=0.0, rot=None,
+                      write_cache=True):
+    """Query and key norm, position rotation and the append of keys and values to the cache, for an attention
+    whose heads have M score maps (csrc/attention_maps.cu).
+
+    buf [T, N]: per token H*M query vectors of Dk at offsets[0], G*M key vectors of Dk at offsets[1], G value
+    vectors of Dv at offsets[2] (which may be the keys' own place: values that are the keys as projected).
+    The queries are rewritten in place; keys and values go to `cache` (a KVLayerView whose key pages are
+    [n_pages, G*M, page, Dk] and value pages [n_pages, G, page, Dv])."""
+    k_pages, v_pages, table = cache.k, cache.v, cache.block_table
+    cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
+    _cuda(buf, k_pages, v_pages, table, q_weight, k_weight, cos, sin)
+    T = ctx.n_tokens
+    off_q, off_k, off_v = (int(o) for o in offsets)
+    N = buf.shape[-1]
+    _need(buf.is_contiguous() and buf.numel() >= T * N and min(off_q, off_k, off_v) >= 0
+          and max(off_q + H * M * Dk, off_k + G * M * Dk, off_v + G * Dv) <= N,
+          "attention_prepare: buf [T, N] must hold the query, key and value vectors at their offsets")
+    _need(0 < Dk <= ATTENTION_MAPS_MAX_DIM and 0 < Dv <= ATTENTION_MAPS_MAX_DIM,
+          f"attention_prepare: head sizes {Dk}, {Dv} are outside 1..{ATTENTION_MAPS_MAX_DIM}")
+    page = k_pages.shape[2]
+    _need(k_pages.dtype == buf.dtype and v_pages is not None and v_pages.dtype == buf.dtype and k_pages.is_contiguous()
+          and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (G * M, page, Dk)
+          and tuple(v_pages.shape[1:]) == (G, page, Dv) and v_pages.shape[0] == k_pages.shape[0],
+          f"attention_prepare: cache pages [n, {G * M}, page, {Dk}] and [n, {G}, page, {Dv}] of buf's dtype")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+          and ctx.max_kv_len <= table.shape[1] * page, "attention_prepare: the block table does not cover the step")
+    for wgt in (q_weight, k_weight):
+        if wgt is not None:
+            _need(wgt.dtype == torch.float32 and wgt.numel() == Dk and wgt.is_contiguous(),
+                  "attention_prepare: norm weights float32 [Dk]")
+    if cos is not None:
+        _need(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+              and sin.is_contiguous() and cos.shape == sin.shape and cos.shape[-1] == n_rot // 2 and n_rot % 2 == 0
+              and 0 < n_rot <= Dk, "attention_prepare: rope tables float32 [P, n_rot/2], n_rot even and at most Dk")
+        _need(ctx.max_kv_len <= cos.shape[0],
+              f"rope tables hold {cos.shape[0]} positions, the step reaches position {ctx.max_kv_len}")
+    _i32(ctx.tok_pos, T, "tok_pos")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _check(_lib("attention_maps").ab_attention_prepare(
+        _p(buf), _dt(buf), N, off_q, off_k, off_v, H * M, G * M, G, Dk, Dv, _p(q_weight), _p(k_weight),
+        ctypes.c_float(eps), _p(cos), _p(sin), n_rot, pairing, _p(ctx.tok_pos), _p(ctx.tok_seq), _p(table),
+        table.shape[1], _p(k_pages), _p(v_pages), page, T, 1 if write_cache else 0, _stream()), "attention_prepare")
+
+
+def attention_maps(q, q_stride, out, cache, ctx, H, G, M, Dk, Dv, scale, window=0, sink=None, coef=0.0,
+                   unit_norm=False, eps=0.0, out_scale=1.0):
+    """Attention of every token over its sequence's cached keys and values, one warp per (token, head), 32-bit
+    arithmetic (csrc/attention_maps.cu): M score maps per head, combined as a_0 + coef * (a_1 + ..), optionally
+    divided by the head's root mean square, times `out_scale`.  q: the prepared rows (query vectors at the
+    start of each row of `q_stride` elements); out [T, H*Dv] of q's dtype."""
+    k_pages, v_pages, table = cache.k, cache.v, cache.block_table
+    _cuda(q, out, k_pages, v_pages, table, sink)
+    T = ctx.n_tokens
+    _need(q.is_contiguous() and out.is_contiguous() and out.dtype == q.dtype and k_pages.dtype == q.dtype
+          and v_pages.dtype == q.dtype and q.numel() >= T * q_stride and q_stride >= H * M * Dk
+          and out.shape[-1] == H * Dv and out.numel() >= T * H * Dv,
+          "attention_maps: q [T, stride], out [T, H*Dv] and the cache share one dtype")
+    _need(0 < Dk <= ATTENTION_MAPS_MAX_DIM and 0 < Dv <= ATTENTION_MAPS_MAX_DIM and H % G == 0 and M >= 1,
+          f"attention_maps: sizes {Dk}, {Dv} (1..{ATTENTION_MAPS_MAX_DIM}) or heads {H}/{G} not supported")
+    page = k_pages.shape[2]
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (G * M, page, Dk)
+          and tuple(v_pages.shape[1:]) == (G, page, Dv), "attention_maps: cache pages [n, G*M, page, Dk], [n, G, page, Dv]")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+          and ctx.max_kv_len <= table.shape[1] * page, "attention_maps: the block table does not cover the step")
+    if sink is not None:
+        _need(sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous(), "sink must be float32 [H]")
+    _i32(ctx.tok_pos, T, "tok_pos")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _check(_lib("attention_maps").ab_attention_maps(
+        _p(q), q_stride, _p(out), _dt(q), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
+        _p(ctx.tok_seq), T, H, G, M, Dk, Dv, page, ctypes.c_float(scale), int(window or 0), _p(sink),
+        ctypes.c_float(coef), 1 if unit_norm else 0, ctypes.c_float(eps), ctypes.c_float(out_scale), _stream()),
+        "attention_maps")
+    return out
+
+
+def attention_sink_mma_supports(H, G, D, dtype) -> bool:
+    """Whether `attention_sink_mma` takes these sizes (the tensor-core kernels of csrc/attention_mma.cu)."""
+    return dtype == torch.bfloat16 and D % 16 == 0 and 0 < D <= 256 and H % G == 0 and H // G <= 64
+
+
+def attention_sink_mma(q, q_stride, out, cache, ctx, H, G, D, scale, window=0, sink=None):
+    """Attention with one score map and values of the keys' size on the tensor-core kernels, with a window and
+    an optional sink per head; q holds the prepared query vectors at the start of each row, keys and values are
+    in the cache already.  bfloat16."""
+    k_pages, v_pages, table = cache.k, cache.v, cache.block_table
+    _cuda(q, out, k_pages, v_pages, table, sink)
+    T = ctx.n_tokens
+    _need(attention_sink_mma_supports(H, G, D, q.dtype), f"attention_sink_mma: {H}/{G} heads of {D} dims not supported")
+    _need(out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous()
+          and q.numel() >= T * q_stride and q_stride >= H * D and q_stride % 8 == 0 and out.shape[-1] == H * D
+          and out.numel() >= T * H * D, "attention_sink_mma: q [T, stride], out [T, H*D], bfloat16")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (G, 64, D)
+          and k_pages.shape == v_pages.shape, "attention_sink_mma: cache pages [n_pages, G, 64, D]")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+          and ctx.max_kv_len <= table.shape[1] * 64, "attention_sink_mma: the block table does not cover the step")
+    if sink is not None:
+        _need(sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous(), "sink must be float32 [H]")
+    lib = _lib("attention_mma")
+    if ctx.is_decode:
+        width = max(int(table.shape[1]), 1)
+        small, n_chunks = _decode_attention_plan(T * G * -(-(H // G) // 8), width, D, _sm_count(q.device))
+        _i32(ctx.tok_seq, T, "tok_seq")
+        _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
+        _check(lib.ab_attention_decode_sink_bf16(
+            _p(q), q_stride, _p(out), None, None, None, _p(k_pages), _p(v_pages), _p(table), table.shape[1],
+            _p(ctx.tok_seq), _p(ctx.kv_len), T, H, G, D, ctypes.c_float(scale), int(window or 0),
+            -(-width // n_chunks), n_chunks, small, None, None, 0, 0, 0, _p(sink), _stream()), "attention_decode")
+        return out
+    _i32(ctx.tok_pos, T, "tok_pos")
+    _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+    tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // G, q.device)
+    _check(lib.ab_attention_prefill_sink_bf16(
+        _p(q), q_stride, _p(out), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos), _p(ctx.cu_q),
+        _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, D, ctypes.c_float(scale), int(window or 0), _p(sink),
+        _stream()), "attention_prefill")
+    return out
+
+
+def add_row(residual, row, ctx):
+    """residual[t, :] += row[:] for every token of the step (float32)."""
+    _cuda(residual, row)
+    E, T = residual.shape[-1], ctx.n_tokens
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and residual.numel() >= T * E
+          and row.dtype == torch.float32 and row.is_contiguous() and row.numel() == E,
+          "add_row: residual float32 [T, E], row float32 [E]")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _check(_lib("stream_ops").ab_add_row(_p(residual), _p(row), _p(ctx.tok_seq), T, E, _stream()), "add_row")
+    return residual
+
+
+def stream_cast(residual, delta, out, n_rows=None):
+    """residual += delta (when given); out = residual in the activation dtype."""
+    _cuda(residual, delta, out)
+    E = residual.shape[-1]
+    n = residual.numel() // E if n_rows is None else n_rows
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and residual.numel() >= n * E
+          and out.is_contiguous() and out.shape[-1] == E and out.numel() >= n * E,
+          "stream_cast: residual float32 [T, E], out [T, E]")
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.dtype == out.dtype and delta.shape[-1] == E and delta.numel() >= n * E,
+              "stream_cast: delta [T, E] of out's dtype")
+    _check(_lib("stream_ops").ab_stream_cast(_p(residual), _p(delta), _p(out), _dt(out), n, E, _stream()), "stream_cast")
+    return out
+
+
+def token_gate(z, table, offset, ctx, out):
+    """out[t, j] = gelu_tanh(z[t, j]) * table[token_t, offset + j]; z, out [T, dim], table [V, W] of one dtype."""
+    _cuda(z, table, out)
+    T, dim = ctx.n_tokens, z.shape[-1]
+    _need(z.is_contiguous() and out.is_contiguous() and table.is_contiguous() and table.dim() == 2
+          and z.dtype == table.dtype == out.dtype and out.shape[-1] == dim and z.numel() >= T * dim
+          and out.numel() >= T * dim and 0 <= offset and offset + dim <= table.shape[1],
+          "token_gate: z, out [T, dim] and table [V, W] of one dtype, offset + dim <= W")
+    _i32(ctx.tokens, T, "tokens")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _check(_lib("stream_ops").ab_token_gate(_p(z), _p(table), table.shape[1], int(offset), _p(ctx.tokens),
+                                            _p(ctx.tok_seq), _p(out), _dt(z), T, dim, _stream()), "token_gate")
+    return out
+
+
+def add_unit_norm(residual, y, weight, eps, ctx):
+    """residual[t, :] += y[t, :] / rms(y[t, :]) * weight for every token of the step (all float32)."""
+    _cuda(residual, y, weight)
+    E, T = residual.shape[-1], ctx.n_tokens
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and residual.numel() >= T * E
+          and y.dtype == torch.float32 and y.is_contiguous() and y.shape[-1] == E and y.numel() >= T * E
+          and weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == E,
+          "add_unit_norm: residual, y float32 [T, E], weight float32 [E]")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _check(_lib("stream_ops").ab_add_unit_norm(_p(residual), _p(y), _p(weight), _p(ctx.tok_seq), T, E,
+                                               ctypes.c_float(eps), _stream()), "add_unit_norm")
+    return residual

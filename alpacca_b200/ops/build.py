@@ -140,7 +140,7 @@ def load(name: str) -> ctypes.CDLL:
 
 
 ALL_LIBRARIES = ("elementwise", "attention_simt", "attention_mma", "gemm_f32", "gemv_bf16", "gemm_tc", "attention_tc", "attention_stream", "sampling", "safetensors_reader",
-                 "mlstm", "latent_attention", "moe")
+                 "mlstm", "latent_attention", "moe", "linear_attention", "attention_maps", "stream_ops")
 
 
 def build_all(names=ALL_LIBRARIES) -> list[Path]:

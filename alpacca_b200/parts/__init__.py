@@ -6,10 +6,14 @@ from .experts import RoutedExperts
 from .feedforward import SwiGLU
 from .latent_attention import LatentAttention
 from .linear import Linear
+from .linear_attention import DecayLinearAttention
+from .maps_attention import MapsAttention
 from .mlstm import MatrixMemory
 from .norm import RMSNorm
 from .position import RotaryEncoding, scaled_inv_freq
+from .stream import PassOffset, TokenSide, TokenTable
 
 __all__ = ["Attention", "Block", "BuildOptions", "FeedForward", "KVSpec", "Mixer", "Norm", "Part", "PositionEncoding",
            "StateSpec", "HiddenStream", "PreNormBlock", "ParallelBlock", "RoutedExperts", "LatentAttention", "MatrixMemory", "TokenEmbedding", "VocabHead", "SwiGLU", "Linear",
-           "RMSNorm", "RotaryEncoding", "scaled_inv_freq"]
+           "RMSNorm", "RotaryEncoding", "scaled_inv_freq", "DecayLinearAttention", "MapsAttention", "PassOffset", "TokenSide",
+           "TokenTable"]

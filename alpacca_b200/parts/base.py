@@ -47,11 +47,23 @@ class BuildOptions:
 class KVSpec:
     """The mixer keeps keys and values of `n_kv_heads` x `head_dim` per token;
     `window` = how many of the latest keys it reads (None: all).  `values` off: one row per token and
-    head only (a mixer whose values are part of its key rows, such as a cached latent)."""
+    head only (a mixer whose values are part of its key rows, such as a cached latent).  `value_heads`,
+    `value_dim`: the values' own head count and size where they differ from the keys' (several key heads
+    that share one value head; values wider or narrower than keys); None: the keys'."""
     n_kv_heads: int
     head_dim: int
     window: int | None = None
     values: bool = True
+    value_heads: int | None = None
+    value_dim: int | None = None
+
+    @property
+    def v_heads(self) -> int:
+        return self.n_kv_heads if self.value_heads is None else self.value_heads
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)

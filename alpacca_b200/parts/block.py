@@ -28,8 +28,12 @@ class HiddenStream:
 
 
 class PreNormBlock(Block):
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None, ffn: FeedForward | None):
-        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+    """`after`: a part that acts on the stream once the sub-layers are done (`forward(stream, ctx)`; a layer's
+    token input, say).  It reads the stream as it stands, so the last sub-layer's output is not prepared
+    for the next block's norm then."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None, ffn: FeedForward | None, after=None):
+        self.norm1, self.mixer, self.norm2, self.ffn, self.after = norm1, mixer, norm2, ffn, after
 
     def first_norm(self, n_rows: int) -> Norm | None:
         """The norm that reads the stream when this block starts, if in a step of `n_rows` rows the
@@ -40,14 +44,18 @@ class PreNormBlock(Block):
 
     def forward(self, stream: HiddenStream, ctx, cache, write_cache: bool = True) -> None:
         next_norm, stream.next_norm = stream.next_norm, None
+        if self.after is not None:
+            next_norm = None
         h = _normed(self.norm1, stream)
         if self.ffn is None:
             _sublayer(stream, next_norm, self.mixer, h, ctx, cache, write_cache)
-            return
-        after_mixer = self.norm2 if _accepts(self.ffn, ctx.n_tokens) else None
-        _sublayer(stream, after_mixer, self.mixer, h, ctx, cache, write_cache)
-        h = _normed(self.norm2, stream)
-        _sublayer(stream, next_norm, self.ffn, h, ctx)
+        else:
+            after_mixer = self.norm2 if _accepts(self.ffn, ctx.n_tokens) else None
+            _sublayer(stream, after_mixer, self.mixer, h, ctx, cache, write_cache)
+            h = _normed(self.norm2, stream)
+            _sublayer(stream, next_norm, self.ffn, h, ctx)
+        if self.after is not None:
+            self.after.forward(stream, ctx)
 
 
 class ParallelBlock(Block):

@@ -5,9 +5,15 @@ gate and up are held as one matrix, interleaved in groups of 8 rows, so that
 one product feeds the activation kernel.  An inner width that is no multiple of
 8 is padded with zero rows (and zero columns of the down matrix) when the
 weights are loaded: silu(0) * 0 adds nothing.
+
+The activation on the gate is SiLU unless another is named ("relu", "gelu_tanh": act(0) * 0 adds nothing
+either); those run the product and then the activation kernel, where SiLU has the fused forms.
 """
 from __future__ import annotations
 
+import torch
+
+from .. import ops
 from .base import BuildOptions, FeedForward
 from .linear import Linear
 
@@ -15,8 +21,10 @@ from .linear import Linear
 class SwiGLU(FeedForward):
     def __init__(self, opts: BuildOptions, width: int, inner: int, prefix: str, bias: bool = False,
                  names=("gate_proj", "up_proj", "down_proj"), weight_suffix: str = ".weight",
-                 out_dtype=None):
-        self.opts, self.width, self.inner = opts, int(width), int(inner)
+                 out_dtype=None, activation: str = "silu"):
+        if activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {tuple(ops.GATE_ACTIVATIONS)}")
+        self.opts, self.width, self.inner, self.activation = opts, int(width), int(inner), activation
         g, u, d = names
         self.gate_up = Linear(opts, width, [(f"{prefix}.{g}", inner), (f"{prefix}.{u}", inner)], bias=bias,
                               interleave8=True, weight_suffix=weight_suffix, pad_rows_to=8)
@@ -26,9 +34,14 @@ class SwiGLU(FeedForward):
     adds_to_residual = True
 
     def accepts_owed_norm(self, n_rows: int) -> bool:
-        return self.gate_up.accepts_owed_norm(n_rows)
+        return self.activation == "silu" and self.gate_up.accepts_owed_norm(n_rows)
 
     def forward(self, h, ctx, then=None):
         T = ctx.n_tokens
-        act = self.gate_up.forward_swiglu(h, n_rows=T)
+        if self.activation == "silu":
+            act = self.gate_up.forward_swiglu(h, n_rows=T)
+        else:
+            gu = self.gate_up.forward(h, n_rows=T)
+            act = torch.empty((gu.shape[0], self.gate_up.out_features // 2), dtype=gu.dtype, device=gu.device)
+            ops.gated_act(gu, act, self.activation, n_rows=T)
         return self.down.forward(act, n_rows=T, then=then)

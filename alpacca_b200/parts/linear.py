@@ -18,10 +18,11 @@ from .base import BuildOptions, OwedNorm, Part
 class Linear(Part):
     def __init__(self, opts: BuildOptions, in_features: int, sources, bias: bool = False,
                  interleave8: bool = False, out_dtype: torch.dtype | None = None, weight_suffix: str = ".weight",
-                 pad_rows_to: int = 0, pad_in_to: int = 0):
+                 pad_rows_to: int = 0, pad_in_to: int = 0, bias_suffix: str = ".bias"):
         """`sources`: list of (checkpoint prefix, rows); tensors `<prefix>.weight`
         [rows, in] (and `<prefix>.bias` [rows]) are stacked in that order
-        (`weight_suffix` "" for checkpoints that name a matrix by its prefix alone).
+        (`weight_suffix` "" for checkpoints that name a matrix by its prefix alone; `bias_suffix` likewise
+        for the biases).
         `interleave8`: two sources of equal size are interleaved in groups of 8
         rows (8 of the first, 8 of the second, ...), the layout `ops.swiglu` reads.
         `out_dtype` float32 gives float32 results from bfloat16 inputs (logits).
@@ -38,7 +39,7 @@ class Linear(Part):
         self.has_bias = bool(bias)
         self.interleave8 = bool(interleave8)
         self.out_dtype = out_dtype or opts.dtype
-        self.weight_suffix = weight_suffix
+        self.weight_suffix, self.bias_suffix = weight_suffix, bias_suffix
         if interleave8:
             if len(self.sources) != 2 or self.sources[0][1] != self.sources[1][1] or self.sources[0][1] % 8:
                 raise ValueError("interleave8 needs two sources of equal size, a multiple of 8 rows "
@@ -50,7 +51,7 @@ class Linear(Part):
         specs = [ParamSpec(f"{p}{self.weight_suffix}", (r, self.stored_in), "matrix", "normal")
                  for p, r in self.stored_sources]
         if self.has_bias:
-            specs += [ParamSpec(f"{p}.bias", (r,), "vector", "normal") for p, r in self.stored_sources]
+            specs += [ParamSpec(f"{p}{self.bias_suffix}", (r,), "vector", "normal") for p, r in self.stored_sources]
         return specs
 
     def _padded(self, t, rows):
@@ -75,7 +76,7 @@ class Linear(Part):
         self.weight = self._stack([self._padded(fetch(ParamSpec(f"{p}{self.weight_suffix}", (r, self.stored_in), "matrix")), rp)
                                    for (p, r), (_, rp) in zip(self.stored_sources, self.sources)])
         if self.has_bias:
-            self.bias = self._stack([self._padded(fetch(ParamSpec(f"{p}.bias", (r,), "vector")), rp)
+            self.bias = self._stack([self._padded(fetch(ParamSpec(f"{p}{self.bias_suffix}", (r,), "vector")), rp)
                                      for (p, r), (_, rp) in zip(self.stored_sources, self.sources)])
 
     def share_weight(self, tensor: torch.Tensor):

@@ -1,0 +1,121 @@
+"""Grouped-query attention over the paged cache in its wider forms: keys and values of sizes of their own,
+several score maps per head, query and key norm, values that are the keys as projected, a sink, a window.
+
+H query heads share G key/value heads (head h reads group h // (H/G)).  A head has M score maps; its query
+has M vectors of `dim`, a group has M key vectors of `dim` and ONE value vector of `vdim`; the rows of W_q
+and W_k are laid out head by head as [map 0, map 1, ..].  Per map m:
+
+    a_m = softmax_s((q_m . k_m,s) * scale) v_s       over the keys s with 0 <= p - s < window
+
+With `sink`, exp(sink_h) is one more term of every softmax's denominator (no key, no value, not scaled).
+Options, each a constructor argument:
+
+    qk_norm          q and k vectors are divided by their root mean square and multiplied by a weight of size
+                     `dim` (one for all query heads, one for all key heads), before the rotation
+    values_are_keys  there is no W_v: the values are the key vectors as projected, before norm and rotation
+    difference d     M = 2: o = a_0 - lambda a_1 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + d from four
+                     learned vectors of size `dim`; o is then divided by its root mean square over `vdim` (no
+                     weight) and multiplied by 1 - d.  (Ye et al., "Differential Transformer".)
+
+The rotation turns the first n_rot dims of every query and key vector (each map by itself).  In bfloat16 with one
+map, equal key and value sizes and a head size in steps of 16, prompts and decode steps run on the tensor-core
+kernels of csrc/attention_mma.cu; everything else runs csrc/attention_maps.cu (32-bit arithmetic).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+from ..weights.loader import ParamSpec
+from .base import BuildOptions, KVSpec, Mixer, PositionEncoding
+from .linear import Linear
+
+
+class MapsAttention(Mixer):
+    def __init__(self, opts: BuildOptions, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int | None,
+                 position: PositionEncoding | None, prefix: str, scale: float, eps: float, window: int | None = None,
+                 n_maps: int = 1, bias: bool = False, qk_norm: bool = False, values_are_keys: bool = False,
+                 sink: bool = False, difference: float | None = None, names=("q", "k", "v", "o"),
+                 weight_suffix: str = "", bias_suffix: str = ".b", out_dtype=None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{prefix}: {n_heads} heads cannot share {n_kv_heads} key/value heads")
+        self.opts, self.prefix = opts, prefix
+        self.width, self.H, self.G, self.M, self.Dk = int(width), int(n_heads), int(n_kv_heads), int(n_maps), int(dim)
+        self.values_are_keys = bool(values_are_keys)
+        if self.values_are_keys:
+            if self.M != 1 or (vdim is not None and int(vdim) != self.Dk):
+                raise ValueError(f"{prefix}: values that are the keys need one map and a value size equal to the keys'")
+            vdim = self.Dk
+        self.Dv = int(vdim if vdim is not None else dim)
+        if difference is not None and self.M != 2:
+            raise ValueError(f"{prefix}: the difference of maps needs exactly two maps")
+        big = ops.ATTENTION_MAPS_MAX_DIM
+        if not (0 < self.Dk <= big and 0 < self.Dv <= big):
+            raise ValueError(f"{prefix}: head sizes {self.Dk} and {self.Dv} are outside 1..{big}")
+        self.window = int(window) if window else None
+        self.scale, self.eps = float(scale), float(eps)
+        self.position, self.qk_norm, self.has_sink = position, bool(qk_norm), bool(sink)
+        self.difference = None if difference is None else float(difference)
+        q, k, v, o = names
+        self.names = names
+        n_q, n_k = self.H * self.M * self.Dk, self.G * self.M * self.Dk
+        sources = [(f"{prefix}.{q}", n_q), (f"{prefix}.{k}", n_k)]
+        if not self.values_are_keys:
+            sources.append((f"{prefix}.{v}", self.G * self.Dv))
+        self.offsets = (0, n_q, n_q if self.values_are_keys else n_q + n_k)
+        self.qkv = Linear(opts, width, sources, bias=bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
+        self.out = Linear(opts, self.H * self.Dv, [(f"{prefix}.{o}", width)], weight_suffix=weight_suffix,
+                          out_dtype=out_dtype)
+        self.q_weight = self.k_weight = self.sink = None
+        self.coef = 0.0
+
+    def own_param_specs(self):
+        p, (q, k, _, _) = self.prefix, self.names
+        specs = []
+        if self.difference is not None:
+            specs += [ParamSpec(f"{p}.{n}", (self.Dk,), "vector", "normal") for n in ("lq1", "lk1", "lq2", "lk2")]
+        if self.qk_norm:
+            specs += [ParamSpec(f"{p}.{q}.norm", (self.Dk,), "vector", "one_plus_normal"),
+                      ParamSpec(f"{p}.{k}.norm", (self.Dk,), "vector", "one_plus_normal")]
+        if self.has_sink:
+            specs.append(ParamSpec(f"{p}.sink", (self.H,), "vector", "normal"))
+        return specs
+
+    def load_own(self, fetch):
+        got = {s.name[len(self.prefix) + 1:]: fetch(s) for s in self.own_param_specs()}
+        if self.difference is not None:
+            d = {n: got[n].double().cpu() for n in ("lq1", "lk1", "lq2", "lk2")}
+            lam = (math.exp(float((d["lq1"] * d["lk1"]).sum())) - math.exp(float((d["lq2"] * d["lk2"]).sum()))
+                   + self.difference)
+            self.coef = -lam
+        if self.qk_norm:
+            self.q_weight, self.k_weight = got[f"{self.names[0]}.norm"], got[f"{self.names[1]}.norm"]
+        if self.has_sink:
+            self.sink = got["sink"]
+
+    def cache_spec(self):
+        return KVSpec(self.G * self.M, self.Dk, self.window, value_heads=self.G, value_dim=self.Dv)
+
+    def _on_tensor_cores(self, buf) -> bool:
+        return (self.M == 1 and self.Dk == self.Dv and buf.shape[-1] % 8 == 0
+                and ops.attention_sink_mma_supports(self.H, self.G, self.Dk, buf.dtype))
+
+    def forward(self, h, ctx, cache, write_cache: bool = True):
+        T = ctx.n_tokens
+        buf = self.qkv.forward(h, n_rows=T)
+        rot = self.position.rotation() if self.position is not None else None
+        ops.attention_prepare(buf, self.offsets, self.H, self.G, self.M, self.Dk, self.Dv, cache, ctx,
+                              q_weight=self.q_weight, k_weight=self.k_weight, eps=self.eps, rot=rot,
+                              write_cache=write_cache)
+        att = torch.empty((buf.shape[0], self.H * self.Dv), dtype=buf.dtype, device=buf.device)
+        if self._on_tensor_cores(buf):
+            ops.attention_sink_mma(buf, buf.shape[-1], att, cache, ctx, self.H, self.G, self.Dk, self.scale,
+                                   self.window or 0, self.sink)
+            return self.out.forward(att, n_rows=T, start_early=False)
+        unit = self.difference is not None
+        ops.attention_maps(buf, buf.shape[-1], att, cache, ctx, self.H, self.G, self.M, self.Dk, self.Dv, self.scale,
+                           self.window or 0, self.sink, coef=self.coef, unit_norm=unit, eps=self.eps,
+                           out_scale=(1.0 - self.difference) if unit else 1.0)
+        return self.out.forward(att, n_rows=T)
