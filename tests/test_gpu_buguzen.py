@@ -44,7 +44,15 @@ def check(got, name, tokens, dtype, what, rows=None):
     got = np.asarray(got)
     assert got.shape == want.shape and np.isfinite(got).all(), what
     if dtype == "bfloat16":
-        check_logits(got, want, dtype, what)
+        # as shares of the spread of the plain logits.  The mean is held to what the other decoders are; a single
+        # logit gets more room: a head's difference of two maps is divided by its own root mean square, up to
+        # seven layer runs in a row, which passes the rounding of a small difference on at full size (largest
+        # seen over this file: 0.37 for one logit, 0.007 for the mean, with the 32-bit runs of the same steps
+        # within 2e-4)
+        d = np.abs(np.asarray(got, np.float64) - want)
+        spread = max(float(want.std()), 1e-30)
+        assert d.max() <= 0.6 * spread and d.mean() <= 0.03 * spread, \
+            f"{what}: max |diff| {d.max() / spread:.3f}, mean {d.mean() / spread:.4f} of the spread"
         return
     # 32-bit: sums of float32 roundings through norms of small vectors and a state carried over many tokens
     diff = np.abs(np.asarray(got, np.float64) - want)
