@@ -14,6 +14,8 @@
 //             out_scale.  The softmax is the running form, in key order; nothing is shared between warps, so
 //             a token's result does not depend on the rest of the batch.
 //
+//   combine   the last step of `attend` alone, for maps that another kernel has attended (float [T, H*M, Dv]).
+//
 // Key pages [n_pages, G*M, page, Dk], value pages [n_pages, G, page, Dv]; one block table for both.
 // Rotation: the first n_rot dims of a vector, pairing 0 = (2i, 2i+1), 1 = (i, i + n_rot/2); tables
 // float32 [positions, n_rot/2].  (u, v) -> (u cos - v sin, v cos + u sin).
@@ -198,6 +200,63 @@ attention_maps_kernel(AttendArgs a) {
     const int d = lane + 32 * j;
     if (d < Dv) o[d] = from_f32<T>(total[j] * mul);
   }
+}
+
+// a [T, H, M, Dv] float: the maps' outputs; out [T, H, Dv] = (a_0 + coef * sum_{m>0} a_m), optionally divided by
+// its root mean square, times out_scale.  One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+maps_combine_kernel(const float* __restrict__ a, T* __restrict__ out, const int* __restrict__ tok_seq, int n_tokens, int H,
+                    int M, int Dv, float coef, int unit_norm, float eps, float out_scale) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)n_tokens * H) return;
+  const int t = (int)(w / H);
+  T* o = out + (size_t)w * Dv;
+  if (tok_seq[t] < 0) {
+    for (int d = lane; d < Dv; d += 32) o[d] = from_f32<T>(0.f);
+    return;
+  }
+  const float* src = a + (size_t)w * M * Dv;
+  float total[AM_MAX_DIM / 32];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < AM_MAX_DIM / 32; ++j) {
+    const int d = lane + 32 * j;
+    float v = 0.f;
+    if (d < Dv) {
+      v = src[d];
+      for (int m = 1; m < M; ++m) v += coef * src[(size_t)m * Dv + d];
+    }
+    total[j] = v;
+    ss += v * v;
+  }
+  float mul = out_scale;
+  if (unit_norm) mul *= 1.0f / sqrtf(warp_sum(ss) / (float)Dv + eps);
+#pragma unroll
+  for (int j = 0; j < AM_MAX_DIM / 32; ++j) {
+    const int d = lane + 32 * j;
+    if (d < Dv) o[d] = from_f32<T>(total[j] * mul);
+  }
+}
+
+AB_API int ab_maps_combine(const float* a, void* out, int dtype, const int* tok_seq, int n_tokens, int H, int M, int Dv,
+                           float coef, int unit_norm, float eps, float out_scale, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (H <= 0 || M <= 0 || Dv <= 0 || Dv > AM_MAX_DIM) return AB_BAD_ARG;
+  const long long warps = (long long)n_tokens * H;
+  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  if (dtype == AB_F32)
+    ab_launch(maps_combine_kernel<float>, dim3(blocks), dim3(128), 0, stream, a, (float*)out, tok_seq, n_tokens, H, M, Dv,
+              coef, unit_norm, eps, out_scale);
+  else if (dtype == AB_BF16)
+    ab_launch(maps_combine_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, a, (bf16*)out, tok_seq, n_tokens, H, M, Dv,
+              coef, unit_norm, eps, out_scale);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
 }
 
 AB_API int ab_attention_prepare(void* buf, int dtype, int stride, int off_q, int off_k, int off_v, int n_q, int n_k,

@@ -44,12 +44,12 @@ struct RowState {
 
 // One key tile (64 keys) for one warp.
 //   qs: this warp's 16 query rows in shared memory, pitch `pitch` elements
-//   ks, vs: the key and value tile [64][pitch]
+//   ks, vs: the key tile [64][pitch] of D dims and the value tile [64][pitch_v] of Dv dims
 //   pos0/pos1, lo0/lo1: last and first visible key of rows g and g+8; key0: position of the tile's first key
 template <int DMAX>
 __device__ __forceinline__ void attend_tile(RowState<DMAX>& st, const bf16* qs, const bf16* ks, const bf16* vs,
-                                            int pitch, int D, float scale_log2, int key0, int pos0, int pos1,
-                                            int lo0, int lo1, bool need_mask) {
+                                            int pitch, int pitch_v, int D, int Dv, float scale_log2, int key0,
+                                            int pos0, int pos1, int lo0, int lo1, bool need_mask) {
   const int lane = threadIdx.x & 31;
   const int t = lane & 3;
   float s[8][4];
@@ -130,9 +130,9 @@ __device__ __forceinline__ void attend_tile(RowState<DMAX>& st, const bf16* qs, 
     const uint32_t a3 = pack_bf16(s[2 * ks16 + 1][2], s[2 * ks16 + 1][3]);
 #pragma unroll
     for (int dp = 0; dp < DMAX / 16; ++dp) {
-      if (dp * 16 < D) {
+      if (dp * 16 < Dv) {
         uint32_t b0, b1, b2, b3;
-        ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vs + (ks16 * 16 + v_key) * pitch + dp * 16 + v_col));
+        ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vs + (ks16 * 16 + v_key) * pitch_v + dp * 16 + v_col));
         mma_bf16(st.o[2 * dp], a0, a1, a2, a3, b0, b1);
         mma_bf16(st.o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
       }
@@ -171,19 +171,25 @@ __device__ __forceinline__ float sum_with_sink(float l, float m, const float* __
 // ---------------------------------------------------------------------------
 // prefill
 // ---------------------------------------------------------------------------
+// The general form: H query vectors and K key heads of D dims, K / M value heads of Dv dims (M score maps per
+// head: key head kh = g*M + m is map m of group g and reads value head g; its G = H/K query vectors are the
+// vectors (g*G + j)*M + m, j < G: a head's maps lie side by side in a token's row).  M = 1, Dv = D is plain
+// grouped-query attention.  out: bfloat16 [T, H, Dv], or float when out_f32 is set (maps that are combined
+// afterwards).  tok_seq (or null): tiles whose first token has no sequence are skipped (padding rows of a
+// captured step of one token each).  DMAX covers both D and Dv.
 template <int DMAX>
 __global__ void __launch_bounds__(128)
-attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
+attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __restrict__ out_any, int out_f32,
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_pos,
-                         const int* __restrict__ cu_q, const int* __restrict__ tile_seq,
-                         const int* __restrict__ tile_q0, int H, int K, int D, float scale_log2, int window,
-                         int tokens_per_tile, const float* __restrict__ sink) {
+                         const int* __restrict__ cu_q, const int* __restrict__ tok_seq,
+                         const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int H, int K, int M, int D,
+                         int Dv, float scale_log2, int window, int tokens_per_tile, const float* __restrict__ sink) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int pitch = D + 8;
+  const int pitch = D + 8, pitch_v = Dv + 8;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);            // [64][pitch]
   bf16* kbuf = qs + 64 * pitch;                            // [2][64][pitch]
-  bf16* vbuf = kbuf + 2 * 64 * pitch;                      // [2][64][pitch]
+  bf16* vbuf = kbuf + 2 * 64 * pitch;                      // [2][64][pitch_v]
 
   pdl_wait();
   pdl_trigger();
@@ -194,6 +200,8 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
   const int tile = blockIdx.x / K, kh = blockIdx.x - tile * K;
   const int b = tile_seq[tile];
   const int q0 = tile_q0[tile];
+  if (tok_seq != nullptr && tok_seq[q0] < 0) return;
+  const int grp = kh / M, map = kh - grp * M;
   const int q_end = cu_q[b + 1];
   const int n_tok = min(tokens_per_tile, q_end - q0);
   const int n_rows = n_tok * G;
@@ -205,7 +213,7 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
       const int r = c / cpr, cc = c - r * cpr;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (r < n_rows) {
-        const int tok = q0 + r / G, h = kh * G + r % G;
+        const int tok = q0 + r / G, h = (grp * G + r % G) * M + map;
         v = *reinterpret_cast<const uint4*>(qkv + (size_t)tok * q_stride + (size_t)h * D + cc * 8);
       }
       *reinterpret_cast<uint4*>(qs + r * pitch + cc * 8) = v;
@@ -227,8 +235,9 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
 
   auto issue = [&](int kb, int stage) {
     const size_t base = ((size_t)bt[kb] * K + kh) * PAGE * D;
+    const size_t base_v = ((size_t)bt[kb] * (K / M) + grp) * PAGE * Dv;
     load_tile_async(kbuf + stage * 64 * pitch, k_pages + base, D, pitch, tid, 128);
-    load_tile_async(vbuf + stage * 64 * pitch, v_pages + base, D, pitch, tid, 128);
+    load_tile_async(vbuf + stage * 64 * pitch_v, v_pages + base_v, Dv, pitch_v, tid, 128);
     cp_async_commit();
   };
   issue(kb_begin, 0);
@@ -240,8 +249,8 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
     // rows of this warp that exist at all; a warp without rows still joins the barriers
     if (warp * 16 < n_rows) {
       const bool need_mask = (key0 + PAGE - 1 > pos_first) || (window > 0);
-      attend_tile<DMAX>(st, qs + warp * 16 * pitch, kbuf + stage * 64 * pitch, vbuf + stage * 64 * pitch, pitch, D,
-                        scale_log2, key0, pos0, pos1, lo0, lo1, need_mask);
+      attend_tile<DMAX>(st, qs + warp * 16 * pitch, kbuf + stage * 64 * pitch, vbuf + stage * 64 * pitch_v, pitch,
+                        pitch_v, D, Dv, scale_log2, key0, pos0, pos1, lo0, lo1, need_mask);
     }
     __syncthreads();
   }
@@ -252,20 +261,23 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, bf16* __res
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  if (r0 < n_rows) l0 = sum_with_sink(l0, st.m[0], sink, kh * G + r0 % G);
-  if (r1 < n_rows) l1 = sum_with_sink(l1, st.m[1], sink, kh * G + r1 % G);
+  if (r0 < n_rows) l0 = sum_with_sink(l0, st.m[0], sink, grp * G + r0 % G);
+  if (r1 < n_rows) l1 = sum_with_sink(l1, st.m[1], sink, grp * G + r1 % G);
   const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+  const size_t o0 = ((size_t)(q0 + r0 / G) * H + (grp * G + r0 % G) * M + map) * Dv;
+  const size_t o1 = ((size_t)(q0 + r1 / G) * H + (grp * G + r1 % G) * M + map) * Dv;
 #pragma unroll
   for (int dt = 0; dt < DMAX / 8; ++dt) {
-    if (dt * 8 < D) {
+    if (dt * 8 < Dv) {
       const int d = dt * 8 + 2 * t4;
-      if (r0 < n_rows) {
-        bf16* o = out + ((size_t)(q0 + r0 / G) * H + kh * G + r0 % G) * D + d;
-        *reinterpret_cast<uint32_t*>(o) = pack_bf16(st.o[dt][0] * inv0, st.o[dt][1] * inv0);
-      }
-      if (r1 < n_rows) {
-        bf16* o = out + ((size_t)(q0 + r1 / G) * H + kh * G + r1 % G) * D + d;
-        *reinterpret_cast<uint32_t*>(o) = pack_bf16(st.o[dt][2] * inv1, st.o[dt][3] * inv1);
+      if (out_f32) {
+        float* out = reinterpret_cast<float*>(out_any);
+        if (r0 < n_rows) *reinterpret_cast<float2*>(out + o0 + d) = make_float2(st.o[dt][0] * inv0, st.o[dt][1] * inv0);
+        if (r1 < n_rows) *reinterpret_cast<float2*>(out + o1 + d) = make_float2(st.o[dt][2] * inv1, st.o[dt][3] * inv1);
+      } else {
+        bf16* out = reinterpret_cast<bf16*>(out_any);
+        if (r0 < n_rows) *reinterpret_cast<uint32_t*>(out + o0 + d) = pack_bf16(st.o[dt][0] * inv0, st.o[dt][1] * inv0);
+        if (r1 < n_rows) *reinterpret_cast<uint32_t*>(out + o1 + d) = pack_bf16(st.o[dt][2] * inv1, st.o[dt][3] * inv1);
       }
     }
   }
@@ -683,18 +695,20 @@ AB_API int ab_attention_decode_round_keys(int D, int small) {
 }
 AB_API int ab_attention_decode_round_pages(int D) { return ab_attention_decode_round_keys(D, 0) / PAGE; }
 
-// `sink`: float [H] or null (see sum_with_sink).
-AB_API int ab_attention_prefill_sink_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
+// The general form (see the kernel): H query vectors, K key heads of D dims, K / M value heads of Dv dims.
+// `sink`: float [H / M] or null (see sum_with_sink); `tok_seq`: int [n_tokens] or null.
+AB_API int ab_attention_prefill_maps_bf16(const void* qkv, int q_stride, void* out, int out_f32, const void* k_pages,
                                           const void* v_pages, const int* block_table, int table_width,
-                                          const int* tok_pos, const int* cu_q, const int* tile_seq, const int* tile_q0,
-                                          int n_tiles, int tokens_per_tile, int H, int K, int D, float scale, int window,
-                                          const float* sink, cudaStream_t stream) {
+                                          const int* tok_pos, const int* cu_q, const int* tok_seq, const int* tile_seq,
+                                          const int* tile_q0, int n_tiles, int tokens_per_tile, int H, int K, int M, int D,
+                                          int Dv, float scale, int window, const float* sink, cudaStream_t stream) {
   if (n_tiles <= 0) return AB_OK;
-  if (D <= 0 || D > 256 || (D % 16) || H % K || K > 65535) return AB_BAD_ARG;
+  if (D <= 0 || D > 256 || (D % 16) || Dv <= 0 || Dv > 256 || (Dv % 16) || K <= 0 || H % K || K > 65535 || M <= 0 || K % M)
+    return AB_BAD_ARG;
   const int G = H / K;
   if (tokens_per_tile < 1 || tokens_per_tile * G > 64) return AB_BAD_ARG;
-  const int pitch = D + 8;
-  const size_t smem = (size_t)(64 + 4 * 64) * pitch * sizeof(bf16);
+  const int pitch = D + 8, pitch_v = Dv + 8;
+  const size_t smem = ((size_t)(64 + 2 * 64) * pitch + (size_t)2 * 64 * pitch_v) * sizeof(bf16);
   if ((long long)n_tiles * K > 0x7fffffffLL) return AB_BAD_ARG;
   dim3 grid((unsigned)n_tiles * K);
   const float sl = scale * LOG2E;
@@ -704,16 +718,27 @@ AB_API int ab_attention_prefill_sink_bf16(const void* qkv, int q_stride, void* o
                                          (int)smem);                                                               \
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
     ab_launch(attention_prefill_kernel<DM>, grid, dim3(128), smem, stream,                                         \
-        (const bf16*)qkv, q_stride, (bf16*)out, (const bf16*)k_pages, (const bf16*)v_pages, block_table,           \
-        table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, D, sl, window, tokens_per_tile, sink);                \
+        (const bf16*)qkv, q_stride, out, out_f32, (const bf16*)k_pages, (const bf16*)v_pages, block_table,         \
+        table_width, tok_pos, cu_q, tok_seq, tile_seq, tile_q0, H, K, M, D, Dv, sl, window, tokens_per_tile, sink); \
   }
-  switch (dmax_of(D)) {
+  switch (dmax_of(D > Dv ? D : Dv)) {
     case 64: AB_GO(64); break;
     case 128: AB_GO(128); break;
     default: AB_GO(256); break;
   }
 #undef AB_GO
   return ab_launch_status();
+}
+
+// `sink`: float [H] or null (see sum_with_sink).
+AB_API int ab_attention_prefill_sink_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,
+                                          const void* v_pages, const int* block_table, int table_width,
+                                          const int* tok_pos, const int* cu_q, const int* tile_seq, const int* tile_q0,
+                                          int n_tiles, int tokens_per_tile, int H, int K, int D, float scale, int window,
+                                          const float* sink, cudaStream_t stream) {
+  return ab_attention_prefill_maps_bf16(qkv, q_stride, out, 0, k_pages, v_pages, block_table, table_width, tok_pos, cu_q,
+                                        nullptr, tile_seq, tile_q0, n_tiles, tokens_per_tile, H, K, 1, D, D, scale, window,
+                                        sink, stream);
 }
 
 AB_API int ab_attention_prefill_bf16(const void* qkv, int q_stride, void* out, const void* k_pages,

@@ -8,11 +8,15 @@
 // by a weight and by sigmoid(g_t).  The state, the decay and every sum are 32-bit.
 //
 // Two forms of the walk over the tokens share one entry point and give the same sums up to rounding:
-//   walk     one CTA per (sequence, head, 32 columns of S): a column's D entries are spread over the registers
-//            of 4 threads (4 warps, each holding a quarter of the rows for 32 columns); q and k of 8 tokens at
-//            a time are brought to shared memory with the activation applied; a thread leaves its share of
-//            S^T q in shared memory, and the four shares are added in a fixed order after the batch's last token;
-//   chunks   (prompts) see the second half of this file.
+//   walk     (steps of a few tokens per sequence) one CTA per (sequence, head, 32 columns of S): a column's D
+//            entries are spread over the registers of 4 threads (4 warps, each holding a quarter of the rows for
+//            32 columns); q and k of 8 tokens at a time are brought to shared memory with the activation
+//            applied; a thread leaves its share of S^T q in shared memory, and the four shares are added in a
+//            fixed order after the batch's last token;
+//   stream   (prompts) a kernel first applies the activation to q | k | v in place; then one CTA per (sequence,
+//            head, 8 or 32 columns) with a column spread over 16 or 4 threads, and the activated rows of 8 or 16
+//            tokens at a time arriving in shared memory by cp.async, two buffers, so that the walk does not
+//            wait for memory and one sequence spreads over many processors.
 // The state of a sequence is read when the step starts and written back when it ends, so a prompt may be cut
 // anywhere and a decode step is the same code with one token.  The projections come as one float32 row per
 // token: zq | zk | zv | g at given offsets.
@@ -112,6 +116,134 @@ linattn_walk_kernel(LinAttnArgs a) {
   }
 }
 
+// silu in place on the columns [c0, c1) of every row that has a sequence
+__global__ void linattn_activate_kernel(float* __restrict__ proj, int ld, int c0, int c1, const int* __restrict__ tok_seq,
+                                        int n_tokens) {
+  pdl_wait();
+  pdl_trigger();
+  const int w = c1 - c0;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_tokens * w) return;
+  const size_t t = i / w;
+  if (tok_seq[t] < 0) return;
+  float* p = proj + t * ld + c0 + (i - t * w);
+  *p = silu_f(*p);
+}
+
+__device__ __forceinline__ void la_cp_async_16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void la_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void la_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// The walk over activated rows.  DPT rows of S per thread, SL threads per column, 128 / SL columns per CTA, TB tokens
+// per buffer.  Needs D, the offsets and ld to be multiples of 4 (16-byte pieces).
+template <int DPT, int SL, int TB>
+__global__ void __launch_bounds__(128)
+linattn_stream_kernel(LinAttnArgs a) {
+  constexpr int COLS = 128 / SL, DP = DPT * SL;
+  extern __shared__ __align__(16) float la_smem[];
+  float* qs = la_smem;                        // [2][TB][DP]
+  float* ks = qs + 2 * TB * DP;               // [2][TB][DP]
+  float* vs = ks + 2 * TB * DP;               // [2][TB][COLS]
+  float* part = vs + 2 * TB * COLS;           // [TB][SL][COLS]
+  pdl_wait();
+  pdl_trigger();
+  const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
+  const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
+  const int slot = a.slots[b];
+  if (slot < 0 || t1 <= t0 || a.tok_seq[t0] < 0) return;
+  const int tid = threadIdx.x, c = tid % COLS, r = tid / COLS;
+  const int D = a.D, V = a.V, col = c0 + c;
+  const float lam = a.decay[h];
+  float* st = a.state + ((size_t)slot * a.H + h) * (size_t)D * V;
+  float s[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = r * DPT + i;
+    s[i] = (d < D && col < V) ? st[(size_t)d * V + col] : 0.f;
+  }
+  // rows of S past D meet zeros: the padding of both buffers is cleared once and never written again
+  for (int i = tid; i < 2 * TB * DP; i += 128) { qs[i] = 0.f; ks[i] = 0.f; }
+  for (int i = tid; i < 2 * TB * COLS; i += 128) vs[i] = 0.f;
+  __syncthreads();
+  const int d4 = D >> 2;
+  auto issue = [&](int tb, int stage) {
+    const int n = min(TB, t1 - tb);
+    for (int i = tid; i < n * d4; i += 128) {
+      const int tok = i / d4, piece = i - tok * d4;
+      const float* row = a.proj + (size_t)(tb + tok) * a.ld + h * D + piece * 4;
+      la_cp_async_16(qs + (stage * TB + tok) * DP + piece * 4, row + a.off_q);
+      la_cp_async_16(ks + (stage * TB + tok) * DP + piece * 4, row + a.off_k);
+    }
+    for (int i = tid; i < n * COLS; i += 128) {
+      const int tok = i / COLS, cc = i - tok * COLS;
+      if (c0 + cc < V) vs[(stage * TB + tok) * COLS + cc] = a.proj[(size_t)(tb + tok) * a.ld + a.off_v + h * V + c0 + cc];
+    }
+    la_cp_async_commit();
+  };
+  issue(t0, 0);
+  int stage = 0;
+  for (int tb = t0; tb < t1; tb += TB, stage ^= 1) {
+    const int n = min(TB, t1 - tb);
+    if (tb + TB < t1) { issue(tb + TB, stage ^ 1); la_cp_async_wait<1>(); } else { la_cp_async_wait<0>(); }
+    __syncthreads();
+    const float* qb = qs + stage * TB * DP + r * DPT;
+    const float* kb = ks + stage * TB * DP + r * DPT;
+    for (int tok = 0; tok < n; ++tok) {
+      const float vv = vs[(stage * TB + tok) * COLS + c];
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kb + tok * DP + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qb + tok * DP + i);
+        s[i] = fmaf(lam, s[i], k4.x * vv);
+        acc0 = fmaf(s[i], q4.x, acc0);
+        s[i + 1] = fmaf(lam, s[i + 1], k4.y * vv);
+        acc1 = fmaf(s[i + 1], q4.y, acc1);
+        s[i + 2] = fmaf(lam, s[i + 2], k4.z * vv);
+        acc0 = fmaf(s[i + 2], q4.z, acc0);
+        s[i + 3] = fmaf(lam, s[i + 3], k4.w * vv);
+        acc1 = fmaf(s[i + 3], q4.w, acc1);
+      }
+      part[(tok * SL + r) * COLS + c] = acc0 + acc1;
+    }
+    __syncthreads();
+    for (int i = tid; i < n * COLS; i += 128) {
+      const int tok = i / COLS, cc = i - tok * COLS;
+      if (c0 + cc < V) {
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < SL; ++j) sum += part[(tok * SL + j) * COLS + cc];
+        a.o_raw[((size_t)(tb + tok) * a.H + h) * V + c0 + cc] = sum;
+      }
+    }
+    // the next round's first barrier comes before `part` and this stage's buffers are written again
+  }
+  if (a.write_state && col < V) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = r * DPT + i;
+      if (d < D) st[(size_t)d * V + col] = s[i];
+    }
+  }
+}
+
+template <int DPT, int SL, int TB>
+static int launch_stream(const LinAttnArgs& a, int n_seqs, cudaStream_t stream) {
+  constexpr int COLS = 128 / SL, DP = DPT * SL;
+  const size_t smem = (size_t)(4 * TB * DP + 2 * TB * COLS + TB * SL * COLS) * sizeof(float);
+  const unsigned col_tiles = (unsigned)((a.V + COLS - 1) / COLS);
+  if (col_tiles > 65535) return AB_BAD_ARG;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(linattn_stream_kernel<DPT, SL, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;
+  }
+  ab_launch(linattn_stream_kernel<DPT, SL, TB>, dim3((unsigned)n_seqs, (unsigned)a.H, col_tiles), dim3(128), smem, stream, a);
+  return ab_launch_status();
+}
+
 // out[t, j] = o[t, j] / rms(o[t, :]) * weight[j] * sigmoid(g[t, j]) over all H*V values of a token; a block per token
 template <typename T>
 __global__ void linattn_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, int ld, int off_g,
@@ -140,24 +272,47 @@ __global__ void linattn_output_kernel(const float* __restrict__ o_raw, const flo
 
 AB_API int ab_linear_attention_max_dim() { return 64 * LA_SLICES; }
 
+// `stream_from`: steps with more than this many tokens per sequence on average take the `stream` form (it rewrites
+// q | k | v of `proj` in place with their activations).
 AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int off_k, int off_v, int off_g,
                                     const float* decay, float* state, int H, int D, int V, const int* cu_q,
                                     const int* slots, const int* tok_seq, int n_seqs, int n_tokens, float* o_raw,
                                     const float* weight, float eps, void* out, int out_dtype, int write_state,
-                                    cudaStream_t stream) {
+                                    int stream_from, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return AB_OK;
   if (H <= 0 || D <= 0 || V <= 0 || D > 64 * LA_SLICES || H > 65535) return AB_BAD_ARG;
   LinAttnArgs a{proj, ld, off_q, off_k, off_v, off_g, decay, state, H, D, V, cu_q, slots, tok_seq, o_raw, write_state};
   const unsigned col_tiles = (unsigned)((V + LA_COLS - 1) / LA_COLS);
   if (col_tiles > 65535) return AB_BAD_ARG;
-  dim3 grid((unsigned)n_seqs, (unsigned)H, col_tiles), block(LA_COLS * LA_SLICES);
-  const int dpt = (D + LA_SLICES - 1) / LA_SLICES;
-  if (dpt <= 4) ab_launch(linattn_walk_kernel<4>, grid, block, 0, stream, a);
-  else if (dpt <= 8) ab_launch(linattn_walk_kernel<8>, grid, block, 0, stream, a);
-  else if (dpt <= 16) ab_launch(linattn_walk_kernel<16>, grid, block, 0, stream, a);
-  else if (dpt <= 32) ab_launch(linattn_walk_kernel<32>, grid, block, 0, stream, a);
-  else ab_launch(linattn_walk_kernel<64>, grid, block, 0, stream, a);
-  int rc = ab_launch_status();
+  int rc;
+  const bool aligned = D % 4 == 0 && ld % 4 == 0 && off_q % 4 == 0 && off_k % 4 == 0;
+  if (aligned && n_tokens > stream_from * n_seqs) {
+    // prompts: activation in place, then the walk on rows that cp.async brings
+    const int c0 = off_q < off_k ? off_q : off_k, c1 = off_v + H * V;
+    if (!(off_k == off_q + H * D && off_v == off_k + H * D)) return AB_BAD_ARG;   // q | k | v side by side
+    const size_t total = (size_t)n_tokens * (c1 - c0);
+    ab_launch(linattn_activate_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+              const_cast<float*>(proj), ld, c0, c1, tok_seq, n_tokens);
+    rc = ab_launch_status();
+    if (rc) return rc;
+    if (D % 64 == 0 && D <= 64) rc = launch_stream<4, 16, 16>(a, n_seqs, stream);
+    else if (D % 64 == 0 && D <= 128) rc = launch_stream<8, 16, 16>(a, n_seqs, stream);
+    else if (D % 64 == 0) rc = launch_stream<16, 16, 8>(a, n_seqs, stream);
+    else if (D <= 16) rc = launch_stream<4, 4, 16>(a, n_seqs, stream);
+    else if (D <= 32) rc = launch_stream<8, 4, 16>(a, n_seqs, stream);
+    else if (D <= 64) rc = launch_stream<16, 4, 16>(a, n_seqs, stream);
+    else if (D <= 128) rc = launch_stream<32, 4, 16>(a, n_seqs, stream);
+    else rc = launch_stream<64, 4, 8>(a, n_seqs, stream);
+  } else {
+    dim3 grid((unsigned)n_seqs, (unsigned)H, col_tiles), block(LA_COLS * LA_SLICES);
+    const int dpt = (D + LA_SLICES - 1) / LA_SLICES;
+    if (dpt <= 4) ab_launch(linattn_walk_kernel<4>, grid, block, 0, stream, a);
+    else if (dpt <= 8) ab_launch(linattn_walk_kernel<8>, grid, block, 0, stream, a);
+    else if (dpt <= 16) ab_launch(linattn_walk_kernel<16>, grid, block, 0, stream, a);
+    else if (dpt <= 32) ab_launch(linattn_walk_kernel<32>, grid, block, 0, stream, a);
+    else ab_launch(linattn_walk_kernel<64>, grid, block, 0, stream, a);
+    rc = ab_launch_status();
+  }
   if (rc) return rc;
   const int n = H * V;
   const int threads = n >= 1024 ? 256 : 128;

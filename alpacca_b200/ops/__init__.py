@@ -1198,13 +1198,17 @@ def linear_attention_max_dim() -> int:
     return 256
 
 
+LINEAR_ATTENTION_STREAM_FROM = 32     # tokens per sequence (on average) from which a step takes the form for prompts
+
+
 def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight, eps, out, write_state=True):
     """Linear attention with a fixed decay per head over the step's tokens, from each sequence's state to its
     new state (csrc/linear_attention.cu).
 
     proj float32 [T, N]: one row per token with zq | zk | zv | g at `offsets` (four column offsets, before the
     activation); decay float32 [H]; state float32 [slots, H, D, V]; out [T, H*V] of the activation dtype gets
-    o / rms(o over all heads) * norm_weight * sigmoid(g)."""
+    o / rms(o over all heads) * norm_weight * sigmoid(g).  `proj` is scratch: a long step leaves the activations
+    in it."""
     _cuda(proj, decay, state, norm_weight, out)
     T, B = ctx.n_tokens, ctx.n_seqs
     off_q, off_k, off_v, off_g = (int(o) for o in offsets)
@@ -1230,7 +1234,8 @@ def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight
     _check(_lib("linear_attention").ab_linear_attention_step(
         _p(proj), ld, off_q, off_k, off_v, off_g, _p(decay), _p(state), H, D, V, _p(ctx.cu_q), _p(ctx.slots),
         _p(ctx.tok_seq), B, T, _p(o_raw), _p(norm_weight), ctypes.c_float(eps), _p(out), _dt(out),
-        1 if write_state else 0, _stream()), "linear_attention_step", kernels=2)
+        1 if write_state else 0, LINEAR_ATTENTION_STREAM_FROM, _stream()), "linear_attention_step",
+        kernels=3 if T > LINEAR_ATTENTION_STREAM_FROM * B else 2)
     return out
 
 
@@ -1314,46 +1319,80 @@ def attention_maps(q, q_stride, out, cache, ctx, H, G, M, Dk, Dv, scale, window=
     return out
 
 
-def attention_sink_mma_supports(H, G, D, dtype) -> bool:
-    """Whether `attention_sink_mma` takes these sizes (the tensor-core kernels of csrc/attention_mma.cu)."""
-    return dtype == torch.bfloat16 and D % 16 == 0 and 0 < D <= 256 and H % G == 0 and H // G <= 64
+def attention_maps_mma_supports(H, G, M, Dk, Dv, stride, dtype) -> bool:
+    """Whether `attention_maps_mma` takes these sizes (the tensor-core kernels of csrc/attention_mma.cu):
+    bfloat16, key and value sizes in steps of 16 up to 256, up to 64 heads per key/value head, rows that start on
+    16 bytes."""
+    return (dtype == torch.bfloat16 and Dk % 16 == 0 and Dv % 16 == 0 and 0 < Dk <= 256 and 0 < Dv <= 256
+            and H % G == 0 and H // G <= 64 and M >= 1 and stride % 8 == 0)
 
 
-def attention_sink_mma(q, q_stride, out, cache, ctx, H, G, D, scale, window=0, sink=None):
-    """Attention with one score map and values of the keys' size on the tensor-core kernels, with a window and
-    an optional sink per head; q holds the prepared query vectors at the start of each row, keys and values are
-    in the cache already.  bfloat16."""
+_ROW_INDEX: dict = {}
+
+
+def _row_index(device, n: int):
+    """int32 [0, 1, .., n-1] on the device (kept: captured steps read it again)."""
+    key = (device.type, device.index)
+    held = _ROW_INDEX.get(key)
+    if held is None or held.numel() < n:
+        if held is not None:
+            _OUTGROWN.append(held)
+        held = torch.arange(max(n, 1024), dtype=torch.int32, device=device)
+        _ROW_INDEX[key] = held
+    return held
+
+
+def attention_maps_mma(q, q_stride, out, cache, ctx, H, G, M, Dk, Dv, scale, window=0, sink=None, coef=0.0,
+                       unit_norm=False, eps=0.0, out_scale=1.0):
+    """`attention_maps` on the tensor-core kernels (bfloat16 operands, float32 scores, softmax and sums): q holds
+    the prepared query vectors at the start of each row, keys and values are in the cache already.  One map with
+    equal key and value sizes in a step of one token each takes the decode kernel; everything else the kernel that
+    tiles query rows (a step of one token each then has one token per tile).  Several maps leave their outputs
+    in float32 and are combined by `ab_maps_combine`."""
     k_pages, v_pages, table = cache.k, cache.v, cache.block_table
     _cuda(q, out, k_pages, v_pages, table, sink)
     T = ctx.n_tokens
-    _need(attention_sink_mma_supports(H, G, D, q.dtype), f"attention_sink_mma: {H}/{G} heads of {D} dims not supported")
-    _need(out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous()
-          and q.numel() >= T * q_stride and q_stride >= H * D and q_stride % 8 == 0 and out.shape[-1] == H * D
-          and out.numel() >= T * H * D, "attention_sink_mma: q [T, stride], out [T, H*D], bfloat16")
-    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (G, 64, D)
-          and k_pages.shape == v_pages.shape, "attention_sink_mma: cache pages [n_pages, G, 64, D]")
+    _need(attention_maps_mma_supports(H, G, M, Dk, Dv, q_stride, q.dtype),
+          f"attention_maps_mma: {H}/{G} heads, {M} maps of {Dk} and {Dv} dims not supported")
+    _need(M > 1 or (not unit_norm and out_scale == 1.0), "attention_maps_mma: one map is left as it is attended")
+    _need(out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16
+          and q.is_contiguous() and out.is_contiguous() and q.numel() >= T * q_stride and q_stride >= H * M * Dk
+          and out.shape[-1] == H * Dv and out.numel() >= T * H * Dv, "attention_maps_mma: q [T, stride], out [T, H*Dv], bfloat16")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (G * M, 64, Dk)
+          and tuple(v_pages.shape[1:]) == (G, 64, Dv) and k_pages.shape[0] == v_pages.shape[0],
+          "attention_maps_mma: cache pages [n_pages, G*M, 64, Dk] and [n_pages, G, 64, Dv]")
     _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
-          and ctx.max_kv_len <= table.shape[1] * 64, "attention_sink_mma: the block table does not cover the step")
+          and ctx.max_kv_len <= table.shape[1] * 64, "attention_maps_mma: the block table does not cover the step")
     if sink is not None:
         _need(sink.dtype == torch.float32 and sink.numel() == H and sink.is_contiguous(), "sink must be float32 [H]")
     lib = _lib("attention_mma")
-    if ctx.is_decode:
+    _i32(ctx.tok_seq, T, "tok_seq")
+    if ctx.is_decode and M == 1 and Dk == Dv:
         width = max(int(table.shape[1]), 1)
-        small, n_chunks = _decode_attention_plan(T * G * -(-(H // G) // 8), width, D, _sm_count(q.device))
-        _i32(ctx.tok_seq, T, "tok_seq")
+        small, n_chunks = _decode_attention_plan(T * G * -(-(H // G) // 8), width, Dk, _sm_count(q.device))
         _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
         _check(lib.ab_attention_decode_sink_bf16(
             _p(q), q_stride, _p(out), None, None, None, _p(k_pages), _p(v_pages), _p(table), table.shape[1],
-            _p(ctx.tok_seq), _p(ctx.kv_len), T, H, G, D, ctypes.c_float(scale), int(window or 0),
+            _p(ctx.tok_seq), _p(ctx.kv_len), T, H, G, Dk, ctypes.c_float(scale), int(window or 0),
             -(-width // n_chunks), n_chunks, small, None, None, 0, 0, 0, _p(sink), _stream()), "attention_decode")
         return out
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
-    tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // G, q.device)
-    _check(lib.ab_attention_prefill_sink_bf16(
-        _p(q), q_stride, _p(out), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos), _p(ctx.cu_q),
-        _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, D, ctypes.c_float(scale), int(window or 0), _p(sink),
-        _stream()), "attention_prefill")
+    if ctx.is_decode:
+        # one token per sequence: a tile per token; the rows are the batch rows themselves
+        tile_seq = tile_q0 = _row_index(q.device, T)
+        n_tiles, tpt = T, 1
+    else:
+        tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // G, q.device)
+    maps = out if M == 1 else torch.empty((q.shape[0], H * M * Dv), dtype=torch.float32, device=q.device)
+    _check(lib.ab_attention_prefill_maps_bf16(
+        _p(q), q_stride, _p(maps), 0 if M == 1 else 1, _p(k_pages), _p(v_pages), _p(table), table.shape[1],
+        _p(ctx.tok_pos), _p(ctx.cu_q), _p(ctx.tok_seq), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H * M, G * M, M, Dk, Dv,
+        ctypes.c_float(scale), int(window or 0), _p(sink), _stream()), "attention_prefill")
+    if M > 1:
+        _check(_lib("attention_maps").ab_maps_combine(
+            _p(maps), _p(out), _dt(out), _p(ctx.tok_seq), T, H, M, Dv, ctypes.c_float(coef),
+            1 if unit_norm else 0, ctypes.c_float(eps), ctypes.c_float(out_scale), _stream()), "maps_combine")
     return out
 
 

@@ -17,9 +17,10 @@ Options, each a constructor argument:
                      learned vectors of size `dim`; o is then divided by its root mean square over `vdim` (no
                      weight) and multiplied by 1 - d.  (Ye et al., "Differential Transformer".)
 
-The rotation turns the first n_rot dims of every query and key vector (each map by itself).  In bfloat16 with one
-map, equal key and value sizes and a head size in steps of 16, prompts and decode steps run on the tensor-core
-kernels of csrc/attention_mma.cu; everything else runs csrc/attention_maps.cu (32-bit arithmetic).
+The rotation turns the first n_rot dims of every query and key vector (each map by itself).  In bfloat16 with key
+and value sizes in steps of 16, prompts and decode steps run on the tensor-core kernels of csrc/attention_mma.cu
+(several maps leave their outputs in float32, which one more kernel combines); everything else runs
+csrc/attention_maps.cu (32-bit arithmetic).
 """
 from __future__ import annotations
 
@@ -99,8 +100,7 @@ class MapsAttention(Mixer):
         return KVSpec(self.G * self.M, self.Dk, self.window, value_heads=self.G, value_dim=self.Dv)
 
     def _on_tensor_cores(self, buf) -> bool:
-        return (self.M == 1 and self.Dk == self.Dv and buf.shape[-1] % 8 == 0
-                and ops.attention_sink_mma_supports(self.H, self.G, self.Dk, buf.dtype))
+        return ops.attention_maps_mma_supports(self.H, self.G, self.M, self.Dk, self.Dv, buf.shape[-1], buf.dtype)
 
     def forward(self, h, ctx, cache, write_cache: bool = True):
         T = ctx.n_tokens
@@ -110,12 +110,10 @@ class MapsAttention(Mixer):
                               q_weight=self.q_weight, k_weight=self.k_weight, eps=self.eps, rot=rot,
                               write_cache=write_cache)
         att = torch.empty((buf.shape[0], self.H * self.Dv), dtype=buf.dtype, device=buf.device)
-        if self._on_tensor_cores(buf):
-            ops.attention_sink_mma(buf, buf.shape[-1], att, cache, ctx, self.H, self.G, self.Dk, self.scale,
-                                   self.window or 0, self.sink)
-            return self.out.forward(att, n_rows=T, start_early=False)
         unit = self.difference is not None
-        ops.attention_maps(buf, buf.shape[-1], att, cache, ctx, self.H, self.G, self.M, self.Dk, self.Dv, self.scale,
-                           self.window or 0, self.sink, coef=self.coef, unit_norm=unit, eps=self.eps,
-                           out_scale=(1.0 - self.difference) if unit else 1.0)
-        return self.out.forward(att, n_rows=T)
+        attend = ops.attention_maps_mma if self._on_tensor_cores(buf) else ops.attention_maps
+        attend(buf, buf.shape[-1], att, cache, ctx, self.H, self.G, self.M, self.Dk, self.Dv, self.scale,
+               self.window or 0, self.sink, coef=self.coef, unit_norm=unit, eps=self.eps,
+               out_scale=(1.0 - self.difference) if unit else 1.0)
+        # after a kernel that fills the processors' shared memory the product starts when that kernel has ended
+        return self.out.forward(att, n_rows=T, start_early=False)

@@ -31,6 +31,8 @@ sequence at a time: it takes the sequences one after another) and prints the sam
 `--design lefatar` leaves the workload above alone and measures the Lefatar decoder (matrix-memory and
 latent-attention layers, dense and routed feed-forwards) beside the Llama decoder of the same width, depth and
 dense feed-forward: one prompt of 2,048 tokens and decode at batch 8 from 512-token prompts, at two sizes.
+`--design buguzen` does the same for the Buguzen decoder (linear attention with a fixed decay, attention with
+two score maps, attention over its own keys, token inputs, two layers that run twice).
 
 One JSON line goes to standard output.  With --gpus N > 1 it prints a line that says so and exits
 with 2: this library runs on one GPU.
@@ -537,7 +539,7 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------------------
-# --design lefatar: the Lefatar decoder beside the Llama decoder of the same width, depth and dense
+# --design lefatar | buguzen: that decoder beside the Llama decoder of the same width, depth and dense
 # feed-forward, at sizes that resemble a real model's layers (random weights).
 
 def _lefatar_layers(E, mlstm, latent, dense_ff, moe, n_layers):
@@ -558,24 +560,56 @@ DESIGN_SIZES = {
               "mlstm": {"heads": 4, "dim": 128, "vdim": 256, "gate_cap": 12.0},
               "latent": {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "q_rank": 384, "kv_rank": 224,
                          "scale": 96 ** -0.5, "rot": {"base": 10000.0, "dims": 32}},
-              "moe": _moe(704, 8, 2, 2, 1)},
+              "moe": _moe(704, 8, 2, 2, 1),
+              "buguzen": {"lin_heads": 8, "lin_dim": 128, "lin_vdim": 128, "diff_heads": 8, "diff_dim": 64, "window": 1024,
+                          "side": 64}},
     "w2048": {"width": 2048, "layers": 8, "vocab": 32000, "dense_ff": 5632, "heads": 16, "kv_heads": 4, "head_dim": 128,
               "mlstm": {"heads": 8, "dim": 128, "vdim": 256, "gate_cap": 12.0},
               "latent": {"heads": 16, "dim": 128, "rot_dim": 32, "vdim": 128, "q_rank": 768, "kv_rank": 224,
                          "scale": 160 ** -0.5, "rot": {"base": 10000.0, "dims": 32}},
-              "moe": _moe(1408, 16, 4, 4, 2)},
+              "moe": _moe(1408, 16, 4, 4, 2),
+              "buguzen": {"lin_heads": 16, "lin_dim": 128, "lin_vdim": 128, "diff_heads": 16, "diff_dim": 64, "window": 1024,
+                          "side": 128}},
 }
 
 
-def design_configs(size):
+def _decays(heads):
+    """A decay per head between 1 - 2^-3 and 1 - 2^-9: short and long memories side by side."""
+    return [1.0 - 2.0 ** -(3.0 + 6.0 * h / max(heads - 1, 1)) for h in range(heads)]
+
+
+def _buguzen_config(z):
+    """Six layers in the pattern (linear attention, attention with two maps, attention over its keys), each with a
+    dense feed-forward and a token input; layers 2 and 3 run twice: eight layer runs, as the Llama decoder beside it."""
+    b = z["buguzen"]
+    dense = {"kind": "dense", "ff": z["dense_ff"]}
+    lightning = {"type": "lightning", "mlp": dense,
+                 "mixer": {"heads": b["lin_heads"], "dim": b["lin_dim"], "vdim": b["lin_vdim"], "decay": _decays(b["lin_heads"])}}
+    diff = {"type": "attention", "mlp": dense,
+            "mixer": {"heads": b["diff_heads"], "kv_heads": z["kv_heads"], "dim": b["diff_dim"], "vdim": 2 * b["diff_dim"],
+                      "scale": b["diff_dim"] ** -0.5, "diff": 0.3, "mask": {"size": b["window"]},
+                      "rot": {"base": 500000.0, "dims": b["diff_dim"] // 2, "scaling": {"factor": 4.0}}}}
+    keys = {"type": "attention_2", "mlp": dense,
+            "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "scale": z["head_dim"] ** -0.5,
+                      "mask": {"size": b["window"]},
+                      "rot": {"base": 1000000.0, "dims": z["head_dim"] // 2,
+                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}}
+    return {"architecture": "Buguzen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [lightning, diff, keys, lightning, diff, keys], "loop": {"start": 2, "stop": 4, "times": 2},
+            "token_side": {"dim": b["side"]}}
+
+
+def design_configs(size, design="lefatar"):
     z = DESIGN_SIZES[size]
-    lefatar = {"architecture": "Lefatar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
-               "layers": _lefatar_layers(z["width"], z["mlstm"], z["latent"], z["dense_ff"], z["moe"], z["layers"])}
     llama = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": z["layers"], "hidden_size": z["width"],
              "num_attention_heads": z["heads"], "num_key_value_heads": z["kv_heads"], "head_dim": z["head_dim"],
              "intermediate_size": z["dense_ff"], "vocab_size": z["vocab"], "max_position_embeddings": 8192,
              "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "rope_pairing": "neox", "tie_word_embeddings": False,
              "hidden_act": "silu"}
+    if design == "buguzen":
+        return {"buguzen": _buguzen_config(z), "llama": llama}
+    lefatar = {"architecture": "Lefatar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+               "layers": _lefatar_layers(z["width"], z["mlstm"], z["latent"], z["dense_ff"], z["moe"], z["layers"])}
     return {"lefatar": lefatar, "llama": llama}
 
 
@@ -602,7 +636,7 @@ def run_design(args):
            "peaks": pk, "sizes": {}}
     for size in ([args.size] if args.size else sorted(DESIGN_SIZES)):
         row = {}
-        for name, cfg in design_configs(size).items():
+        for name, cfg in design_configs(size, args.design).items():
             vocab = cfg.get("vocab") or cfg["vocab_size"]
             shape = {"config": {"vocab_size": vocab}, "prompt_lengths": (prompt_len, prompt_len), "temperature": 0.0}
             context = max(prefill_tokens, prompt_len + steps + max(args.warmup, 3) + 2)
@@ -656,7 +690,7 @@ def main():
                     help="with --only decode: equal prompts of this many tokens instead of the workload's")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="with --only prefill: one prompt of this many tokens instead of the workload's")
-    ap.add_argument("--design", default="", choices=["", "lefatar"],
+    ap.add_argument("--design", default="", choices=["", "lefatar", "buguzen"],
                     help="instead of the benchmark workload: prefill and decode throughput of this design beside the "
                          "Llama decoder of the same width and depth (random weights), one JSON line")
     ap.add_argument("--size", default="", choices=[""] + sorted(DESIGN_SIZES), help="with --design: one size only")

@@ -12,6 +12,10 @@ from helpers import PartHarness, load_part
 pytestmark = pytest.mark.gpu
 
 TOL = {"float32": (2e-4, 2e-5), "bfloat16": (0.12, 0.02)}      # (largest, mean) |difference| as shares of the spread
+# the difference of two maps, divided by its own root mean square, passes the rounding of the maps on at full size
+# (largest seen: 0.13 of the spread for one value, 0.009 for the mean, on the tensor-core kernels, whose softmax
+# weights are bfloat16 in the product with the values)
+TOL_DIFF_BF16 = (0.25, 0.02)
 
 
 def close(got, want, dtype, what, tol=None):
@@ -140,26 +144,27 @@ def test_attention_whole_portions_and_single_tokens(dtype, kind, H, G, D, V, win
     x, x64 = hidden(rng, 150, width, dtype)
     y, y64 = hidden(rng, 40, width, dtype)
     want, want_y = fn(x64, w, mx, eps), fn(y64, w, mx, eps)
+    tol = TOL_DIFF_BF16 if (kind, dtype) == ("diff", "bfloat16") else None
     hs = PartHarness([part.cache_spec()], dtype, max_slots=4)
     for cuts in ((150,), (2, 3, 59, 1, 64, 2, 19), (60,) + (1,) * 90):
         s = hs.cache.alloc_slot()
-        close(feed(part, hs, s, x, cuts), want, dtype, f"attention {kind} in portions {cuts[:4]}")
+        close(feed(part, hs, s, x, cuts), want, dtype, f"attention {kind} in portions {cuts[:4]}", tol=tol)
         hs.cache.free_slot(s)
     s, s2 = hs.cache.alloc_slot(), hs.cache.alloc_slot()
     ctx = hs.step([(s2, 40), (s, 100)])
     view = hs.cache.entry_view(0, ctx.block_tables)
     both = part.forward(torch.cat([y, x[:100]]).contiguous(), ctx, view).float().cpu().numpy()
     hs.done()
-    close(both[:40], want_y, dtype, f"attention {kind}, the short sequence of a batch")
-    close(both[40:], want[:100], dtype, f"attention {kind}, the long sequence of a batch")
+    close(both[:40], want_y, dtype, f"attention {kind}, the short sequence of a batch", tol=tol)
+    close(both[40:], want[:100], dtype, f"attention {kind}, the long sequence of a batch", tol=tol)
     # both go on by one token each in one step
     ctx = hs.step([(s2, 1), (s, 1)])
     view = hs.cache.entry_view(0, ctx.block_tables)
     y2, y2_64 = hidden(rng, 1, width, dtype)
     nxt = part.forward(torch.cat([y2, x[100:101]]).contiguous(), ctx, view).float().cpu().numpy()
     hs.done()
-    close(nxt[1:], want[100:101], dtype, f"attention {kind}, a decode step of two sequences")
-    close(nxt[:1], fn(np.concatenate([y64, y2_64]), w, mx, eps)[40:], dtype, f"attention {kind}, the other row")
+    close(nxt[1:], want[100:101], dtype, f"attention {kind}, a decode step of two sequences", tol=tol)
+    close(nxt[:1], fn(np.concatenate([y64, y2_64]), w, mx, eps)[40:], dtype, f"attention {kind}, the other row", tol=tol)
     hs.cache.check()
 
 
