@@ -37,6 +37,7 @@ struct PrepareArgs {
   const int* block_table; int table_width;
   void* k_pages; void* v_pages; int page_size;
   int n_tokens, write_cache;
+  const float* bias;       // [stride] or null: added to the projected values first (a projection that left it out)
 };
 
 template <typename T>
@@ -59,21 +60,27 @@ attention_prepare_kernel(PrepareArgs a) {
   if (vec >= a.n_q + a.n_k) {                       // a value vector: copied as projected
     if (!a.write_cache) return;
     const int g = vec - a.n_q - a.n_k;
-    const T* src = row + a.off_v + (size_t)g * a.Dv;
+    const int col = a.off_v + g * a.Dv;
+    const T* src = row + col;
     T* dst = reinterpret_cast<T*>(a.v_pages) + (((size_t)page * a.n_v + g) * a.page_size + in_page) * a.Dv;
-    for (int d = lane; d < a.Dv; d += 32) dst[d] = src[d];
+    if (a.bias == nullptr) {
+      for (int d = lane; d < a.Dv; d += 32) dst[d] = src[d];
+    } else {
+      for (int d = lane; d < a.Dv; d += 32) dst[d] = from_f32<T>(to_f32(src[d]) + a.bias[col + d]);
+    }
     return;
   }
   const bool is_q = vec < a.n_q;
   if (!is_q && !a.write_cache) return;
   const int head = is_q ? vec : vec - a.n_q;
   const int D = a.Dk;
-  T* src = row + (is_q ? a.off_q : a.off_k) + (size_t)head * D;
+  const int col = (is_q ? a.off_q : a.off_k) + head * D;
+  T* src = row + col;
   const float* weight = is_q ? a.q_weight : a.k_weight;
   float* x = stage[wib];
   float ss = 0.f;
   for (int d = lane; d < D; d += 32) {
-    const float v = to_f32(src[d]);
+    const float v = to_f32(src[d]) + (a.bias != nullptr ? a.bias[col + d] : 0.f);
     x[d] = v;
     ss += v * v;
   }
@@ -263,13 +270,15 @@ AB_API int ab_attention_prepare(void* buf, int dtype, int stride, int off_q, int
                                 int n_v, int Dk, int Dv, const float* q_weight, const float* k_weight, float eps,
                                 const float* cos_t, const float* sin_t, int n_rot, int pairing, const int* tok_pos,
                                 const int* tok_seq, const int* block_table, int table_width, void* k_pages,
-                                void* v_pages, int page_size, int n_tokens, int write_cache, cudaStream_t stream) {
+                                void* v_pages, int page_size, int n_tokens, int write_cache, const float* bias,
+                                cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (Dk <= 0 || Dk > AM_MAX_DIM || Dv <= 0 || n_q < 0 || n_k < 0 || n_v < 0 || page_size <= 0) return AB_BAD_ARG;
   if (n_rot < 0 || n_rot > Dk || (n_rot & 1) || pairing < 0 || pairing > 1) return AB_BAD_ARG;
   if (!cos_t || !sin_t || n_rot == 0) { cos_t = sin_t = nullptr; n_rot = 0; }
   PrepareArgs a{buf, stride, off_q, off_k, off_v, n_q, n_k, n_v, Dk, Dv, q_weight, k_weight, eps, cos_t, sin_t, n_rot,
-                pairing, tok_pos, tok_seq, block_table, table_width, k_pages, v_pages, page_size, n_tokens, write_cache};
+                pairing, tok_pos, tok_seq, block_table, table_width, k_pages, v_pages, page_size, n_tokens, write_cache,
+                bias};
   const long long warps = (long long)n_tokens * (n_q + n_k + n_v);
   const unsigned blocks = (unsigned)((warps + 3) / 4);
   if (dtype == AB_F32) ab_launch(attention_prepare_kernel<float>, dim3(blocks), dim3(128), 0, stream, a);

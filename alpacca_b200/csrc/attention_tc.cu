@@ -165,7 +165,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_pos,
                             const int* __restrict__ cu_q, const int* __restrict__ tile_seq,
                             const int* __restrict__ tile_q0, int H, int K, float scale_log2, int window,
-                            int tokens_per_tile, int* __restrict__ status) {
+                            int tokens_per_tile, int* __restrict__ status, const float* __restrict__ sink) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   using Sm = AtSmem<HD>;
@@ -372,6 +372,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // a sink: a learned logit per head whose exp joins the denominator and which has no value
+      if (sink != nullptr && row_ok && m_ref > -INFINITY) l_run += exp2f(sink[kh * G + r % G] * AT_LOG2E - m_ref);
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       bf16* dst = out + ((size_t)(q0 + r / G) * H + kh * G + r % G) * HD;
 #pragma unroll
@@ -447,22 +449,26 @@ AB_API int ab_attention_prefill_tc_supports(int H, int K, int D) {
   return H / K <= AT_ROWS ? 1 : 0;
 }
 
-// qkv [n_tokens, (H+2K)*D] (q part read), out [n_tokens, H*D], cache pages [n_pages, K, 64, D].
+// qkv [n_tokens, row_heads * D]: a token's row holds row_heads vectors of D, the first H of them its query heads
+// (q part read); out [n_tokens, H*D], cache pages [n_pages, K, 64, D].  `sink`: float [H] or null, one more term
+// exp(sink_h) in every softmax's denominator.
 // tile_seq / tile_q0: the tiles of floor(128 / G) tokens (sequence, first packed token), as for the mma kernel.
-AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, const void* k_pages, const void* v_pages,
-                                   int n_pages, const int* block_table, int table_width, const int* tok_pos,
-                                   const int* cu_q, const int* tile_seq, const int* tile_q0, int n_tiles, int H,
-                                   int K, int D, float scale, int window, cudaStream_t stream) {
+AB_API int ab_attention_prefill_tc_sink(const void* qkv, int row_heads, int n_tokens, void* out, const void* k_pages,
+                                        const void* v_pages, int n_pages, const int* block_table, int table_width,
+                                        const int* tok_pos, const int* cu_q, const int* tile_seq, const int* tile_q0,
+                                        int n_tiles, int H, int K, int D, float scale, int window, const float* sink,
+                                        cudaStream_t stream) {
   if (n_tiles <= 0) return AB_OK;
-  if (!ab_attention_prefill_tc_supports(H, K, D) || (long long)n_tiles * K > 0x7fffffffLL) return AB_BAD_ARG;
+  if (!ab_attention_prefill_tc_supports(H, K, D) || (long long)n_tiles * K > 0x7fffffffLL || row_heads < H)
+    return AB_BAD_ARG;
   AtEncodeFn enc = at_encode_fn();
   int* status = at_status_word();
   if (!enc || !status) return AB_BAD_ARG;
   const int G = H / K, tpt = AT_ROWS / G;
   CUtensorMap mq, mk, mv;
   {
-    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)(H + 2 * K), (cuuint64_t)n_tokens};
-    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)(H + 2 * K) * D * 2};
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)row_heads, (cuuint64_t)n_tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)row_heads * D * 2};
     cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)tpt};          // one panel: 64 elements of the head
     cuuint32_t elem[3] = {1, 1, 1};
     if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(qkv), dims, strides, box, elem,
@@ -488,10 +494,19 @@ AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, con
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
     e = ab_launch(attention_prefill_tc_kernel<HDV>, dim3((unsigned)n_tiles * K), dim3(AT_THREADS), (size_t)AtSmem<HDV>::TOTAL, \
                   stream, mq, mk, mv, (bf16*)out, block_table, table_width, tok_pos, cu_q, tile_seq, tile_q0, H, K, \
-                  scale * AT_LOG2E, window, tpt, status);                                                           \
+                  scale * AT_LOG2E, window, tpt, status, sink);                                                     \
   }
   if (D == 64) AT_GO(64) else AT_GO(128)
 #undef AT_GO
   if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;
   return ab_launch_status();
+}
+
+// qkv [n_tokens, (H+2K)*D]: q | k | v of a token side by side; no sink.
+AB_API int ab_attention_prefill_tc(const void* qkv, int n_tokens, void* out, const void* k_pages, const void* v_pages,
+                                   int n_pages, const int* block_table, int table_width, const int* tok_pos,
+                                   const int* cu_q, const int* tile_seq, const int* tile_q0, int n_tiles, int H,
+                                   int K, int D, float scale, int window, cudaStream_t stream) {
+  return ab_attention_prefill_tc_sink(qkv, H + 2 * K, n_tokens, out, k_pages, v_pages, n_pages, block_table, table_width,
+                                      tok_pos, cu_q, tile_seq, tile_q0, n_tiles, H, K, D, scale, window, nullptr, stream);
 }

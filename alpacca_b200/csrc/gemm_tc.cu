@@ -45,6 +45,8 @@
 #define EPI_STORE_BF16 0
 #define EPI_STORE_F32 1
 #define EPI_SWIGLU_BF16 2
+#define EPI_RELUGLU_BF16 3      // the same tail with max(g, 0) on the gate
+#define EPI_GELUGLU_BF16 4      // ... with the tanh form of GELU on the gate
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -106,6 +108,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 // far below the bfloat16 rounding of the result): in the tail of a tile, where it runs beside the next
 // tile's MMAs, the exact forms cost 9 us of a 100 us product (2048 x 16384 x 2048), these 3.
 __device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+// the gate's activation of a gated tail: 0.5 g (1 + tanh(u)) = g / (1 + e^(-2u)), u = sqrt(2/pi) (g + 0.044715 g^3)
+template <int EPI>
+__device__ __forceinline__ float gate_fast(float g) {
+  if (EPI == EPI_RELUGLU_BF16) return fmaxf(g, 0.f);
+  if (EPI == EPI_GELUGLU_BF16) return __fdividef(g, 1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
+  return silu_fast(g);
+}
 
 template <int BN> struct TcShape {
   // few columns: the kernel streams weights and is bound by bytes in flight, so a deep ring;
@@ -127,7 +136,7 @@ __device__ __forceinline__ void tail16(const float* v, int row_g, int col0_g, in
   if (!SWAP) {
     const int m = row_g;
     if (m >= rows_total) return;
-    if (EPI == EPI_SWIGLU_BF16) {
+    if (EPI >= EPI_SWIGLU_BF16) {
       // columns col0..col0+7 gate, +8..+15 up of units (col0/16)*8 + 0..7
       if (col0_g + 16 > cols_total) return;
       bf16* y = reinterpret_cast<bf16*>(Y) + (size_t)m * ldy + (col0_g >> 1);
@@ -139,7 +148,7 @@ __device__ __forceinline__ void tail16(const float* v, int row_g, int col0_g, in
         for (int e = 0; e < 2; ++e) {
           const int u = 2 * j + e;
           const float g = v[u] + (bias ? bias[col0_g + u] : 0.f), up = v[8 + u] + (bias ? bias[col0_g + 8 + u] : 0.f);
-          a[e] = silu_fast(g) * up;
+          a[e] = gate_fast<EPI>(g) * up;
         }
         __nv_bfloat162 r = __floats2bfloat162_rn(a[0], a[1]);
         w[j] = *reinterpret_cast<uint32_t*>(&r);
@@ -172,7 +181,7 @@ __device__ __forceinline__ void tail16(const float* v, int row_g, int col0_g, in
     // swapped: this thread's row is feature n; column c is batch row m = col0_g + c
     const int n = row_g;
     const float b = (bias && n < rows_total) ? bias[n] : 0.f;
-    if (EPI == EPI_SWIGLU_BF16) {
+    if (EPI >= EPI_SWIGLU_BF16) {
       // rows 16q..16q+7 gate, 16q+8..16q+15 up: lanes with bit 3 clear hold gates, their partner is lane + 8
       const int unit = (n >> 4) * 8 + (n & 7);
 #pragma unroll
@@ -181,7 +190,7 @@ __device__ __forceinline__ void tail16(const float* v, int row_g, int col0_g, in
         const float partner = __shfl_down_sync(0xffffffffu, mine, 8);
         const int m = col0_g + c;
         if (!(lane & 8) && n < rows_total && m < cols_total)
-          reinterpret_cast<bf16*>(Y)[(size_t)m * ldy + unit] = __float2bfloat16_rn(silu_fast(mine) * partner);
+          reinterpret_cast<bf16*>(Y)[(size_t)m * ldy + unit] = __float2bfloat16_rn(gate_fast<EPI>(mine) * partner);
       }
     } else {
       if (n >= rows_total) return;
@@ -794,7 +803,7 @@ AB_API int ab_gemm_tc(const void* X, const void* W, const float* bias, void* Y, 
                       cudaStream_t stream) {
   if (M <= 0 || N <= 0) return AB_OK;
   if (K <= 0 || (K % 8) || slices < 1) return AB_BAD_ARG;
-  if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
+  if (epilogue_kind >= EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
   if (slices > 1 && (!partials || !arrivals)) return AB_BAD_ARG;
   int* status = status_word();
   if (!status) return AB_BAD_ARG;
@@ -814,12 +823,13 @@ AB_API int ab_gemm_tc(const void* X, const void* W, const float* bias, void* Y, 
   return AB_BAD_ARG;
 }
 
-// The persistent form: Y = X[M,K] . W[N,K]^T for many rows, tiles of 128 x 256, one CTA per processor.
+// The persistent form (epilogue kinds 0 to 4: the gated tails also with ReLU or tanh-GELU on the gate):
+// Y = X[M,K] . W[N,K]^T for many rows, tiles of 128 x 256, one CTA per processor.
 AB_API int ab_gemm_tc_persistent(const void* X, const void* W, const float* bias, void* Y, int M, int N, int K,
                                  int ldy, int epilogue_kind, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return AB_OK;
   if (K <= 0 || (K % 8)) return AB_BAD_ARG;
-  if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
+  if (epilogue_kind >= EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
   int* status = status_word();
   if (!status) return AB_BAD_ARG;
   CUtensorMap mx, mw;
@@ -847,6 +857,8 @@ AB_API int ab_gemm_tc_persistent(const void* X, const void* W, const float* bias
     case EPI_STORE_BF16: AB_GO(EPI_STORE_BF16)
     case EPI_STORE_F32: AB_GO(EPI_STORE_F32)
     case EPI_SWIGLU_BF16: AB_GO(EPI_SWIGLU_BF16)
+    case EPI_RELUGLU_BF16: AB_GO(EPI_RELUGLU_BF16)
+    case EPI_GELUGLU_BF16: AB_GO(EPI_GELUGLU_BF16)
   }
 #undef AB_GO
   return AB_BAD_ARG;
@@ -857,7 +869,7 @@ AB_API int ab_gemm_tc_pair(const void* X, const void* W, const float* bias, void
                            int ldy, int epilogue_kind, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return AB_OK;
   if (K <= 0 || (K % 8)) return AB_BAD_ARG;
-  if (epilogue_kind == EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
+  if (epilogue_kind >= EPI_SWIGLU_BF16 && (N % 16)) return AB_BAD_ARG;
   int* status = status_word();
   if (!status) return AB_BAD_ARG;
   CUtensorMap mx, mw;
@@ -898,6 +910,8 @@ AB_API int ab_gemm_tc_pair(const void* X, const void* W, const float* bias, void
     case EPI_STORE_BF16: AB_GO(EPI_STORE_BF16)
     case EPI_STORE_F32: AB_GO(EPI_STORE_F32)
     case EPI_SWIGLU_BF16: AB_GO(EPI_SWIGLU_BF16)
+    case EPI_RELUGLU_BF16: AB_GO(EPI_RELUGLU_BF16)
+    case EPI_GELUGLU_BF16: AB_GO(EPI_GELUGLU_BF16)
   }
 #undef AB_GO
   return AB_BAD_ARG;

@@ -69,7 +69,14 @@ struct GemvNorm {
   float* residual;        // EPI_RESIDUAL: float32 [M, N], updated in place
   const float* norm_w;    // EPI_RESIDUAL: float32 [N], the weight of the norm that follows
   float* ss_out;          // EPI_RESIDUAL: float32 [M, ceil(N / 16)]
+  int gate_act;           // EPI_SWIGLU: the activation on the gate, 0 SiLU, 1 ReLU, 2 GELU in its tanh form
 };
+
+__device__ __forceinline__ float gate_activation(float g, int kind) {
+  if (kind == 1) return fmaxf(g, 0.f);
+  if (kind == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
 
 __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -123,7 +130,7 @@ __device__ __forceinline__ void epilogue(const float acc[4], int i, int ln, int 
       for (int j = 0; j < 2; ++j) {
         if (m0 + j < M) {
           const float gate = c[j] + bg, up = c[2 + j] + bu;
-          y[(size_t)(m0 + j) * ldy + col] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+          y[(size_t)(m0 + j) * ldy + col] = __float2bfloat16_rn(gate_activation(gate, nf.gate_act) * up);
         }
       }
     }
@@ -376,10 +383,11 @@ AB_API int ab_gemv_bf16_slices(int N, int K, int n_sms) {
 // division by sqrt(sum * inv_width + eps) is applied to this product's sums.
 // slices > 1 needs scratch: partials float [ceil(N/16) * slices * 128 * (1, 2 or 4 for M <= 8, 16, 32)],
 // arrivals int [ceil(N/16)], zero before the first launch and left zero by every launch.
-AB_API int ab_gemv_bf16_norm(const void* X, const void* W, const float* bias, void* Y, float* partials,
-                             int* arrivals, int M, int N, int K, int ldy, int epilogue_kind, int slices,
-                             const float* ss_in, int n_part_in, float inv_width, float eps, float* residual,
-                             const float* norm_w, float* ss_out, cudaStream_t stream) {
+// gate_act (epilogue 2): the activation on the gate, 0 SiLU, 1 ReLU, 2 GELU in its tanh form.
+AB_API int ab_gemv_bf16_gated(const void* X, const void* W, const float* bias, void* Y, float* partials,
+                              int* arrivals, int M, int N, int K, int ldy, int epilogue_kind, int slices,
+                              const float* ss_in, int n_part_in, float inv_width, float eps, float* residual,
+                              const float* norm_w, float* ss_out, int gate_act, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return AB_OK;
   if (M > 32 || K <= 0 || (K % 8) || slices < 1 || slices > 65535) return AB_BAD_ARG;
   if (slices > 1 && (!partials || !arrivals)) return AB_BAD_ARG;
@@ -389,6 +397,8 @@ AB_API int ab_gemv_bf16_norm(const void* X, const void* W, const float* bias, vo
   GemvNorm nf;
   nf.ss_in = ss_in; nf.n_part_in = ss_in ? n_part_in : 0; nf.inv_width = inv_width; nf.eps = eps;
   nf.residual = residual; nf.norm_w = norm_w; nf.ss_out = ss_out;
+  if (gate_act < 0 || gate_act > 2) return AB_BAD_ARG;
+  nf.gate_act = gate_act;
   // few slabs and more than one round of loads per warp: 16 warps per CTA
   const int wide = (M <= 16 && slices == 1 && (N + 15) / 16 <= gemv_sm_count() && K > 8 * GEMV_U * 32) ? 1 : 0;
   switch (epilogue_kind) {
@@ -398,6 +408,14 @@ AB_API int ab_gemv_bf16_norm(const void* X, const void* W, const float* bias, vo
     case EPI_RESIDUAL_BF16: return launch<EPI_RESIDUAL_BF16>(X, W, bias, Y, partials, arrivals, M, N, K, ldy, slices, wide, nf, stream);
   }
   return AB_BAD_ARG;
+}
+
+AB_API int ab_gemv_bf16_norm(const void* X, const void* W, const float* bias, void* Y, float* partials,
+                             int* arrivals, int M, int N, int K, int ldy, int epilogue_kind, int slices,
+                             const float* ss_in, int n_part_in, float inv_width, float eps, float* residual,
+                             const float* norm_w, float* ss_out, cudaStream_t stream) {
+  return ab_gemv_bf16_gated(X, W, bias, Y, partials, arrivals, M, N, K, ldy, epilogue_kind, slices, ss_in, n_part_in,
+                            inv_width, eps, residual, norm_w, ss_out, 0, stream);
 }
 
 AB_API int ab_gemv_bf16(const void* X, const void* W, const float* bias, void* Y, float* partials, int* arrivals,

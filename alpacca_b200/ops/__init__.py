@@ -339,11 +339,12 @@ def _sm_count(device) -> int:
 
 
 def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None, start_early=True, owed=None,
-              residual=None, norm_weight=None):
+              residual=None, norm_weight=None, activation="silu"):
     """out[:n] = x[:n] @ w^T (+ bias) for n <= 32 rows, bfloat16 x [M,K], w [N,K].
 
     out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row interleaved gate|up
-    matrix [2F,K] and out is bfloat16 [M,F] = silu(gate) * up.  `start_early` off: the kernel is
+    matrix [2F,K] and out is bfloat16 [M,F] = act(gate) * up (`activation`: "silu", "relu",
+    "gelu_tanh").  `start_early` off: the kernel is
     launched without programmatic dependent launch, i.e. after the kernel before it has ended (for
     the product that follows the decode attention, see csrc/launch.cuh).
 
@@ -402,10 +403,10 @@ def gemv_bf16(x, w, out, bias=None, n_rows=None, swiglu=False, slices=None, star
     if not start_early:
         lib.ab_pdl_hold(1)
     try:
-        _check(lib.ab_gemv_bf16_norm(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K,
-                                     out.shape[-1], epi, slices, _p(ss_in), n_part, ctypes.c_float(inv_width),
-                                     ctypes.c_float(eps), _p(residual), _p(norm_weight), _p(ss_out), _stream()),
-               "gemv_bf16")
+        _check(lib.ab_gemv_bf16_gated(_p(x), _p(w), _p(bias), _p(out), _p(partials), _p(arrivals), n, N, K,
+                                      out.shape[-1], epi, slices, _p(ss_in), n_part, ctypes.c_float(inv_width),
+                                      ctypes.c_float(eps), _p(residual), _p(norm_weight), _p(ss_out),
+                                      GATE_ACTIVATIONS[activation], _stream()), "gemv_bf16")
     finally:
         if not start_early:
             lib.ab_pdl_hold(0)
@@ -827,11 +828,12 @@ def decode_advance(tokens, tok_pos, kv_len, rng_step, tok_seq, sampled, recent, 
 
 
 def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None, slices=None, persistent=True,
-            pair=None):
+            pair=None, activation="silu"):
     """out[:n] = x[:n] @ w^T (+ bias) on the tcgen05 tensor cores (TMA-fed, TMEM accumulators).
 
     x [M,K], w [N,K] bfloat16; out bfloat16 or float32 [M,N]; with `swiglu`, w is the 8-row
-    interleaved gate|up matrix and out is bfloat16 [M, N/2].  `swap` puts the weights on the
+    interleaved gate|up matrix and out is bfloat16 [M, N/2] (`activation` on the gate: "silu"; "relu" and
+    "gelu_tanh" in the persistent forms only).  `swap` puts the weights on the
     128-row side of the MMA (the batch, up to 256 rows, becomes the columns): the shape for decode
     steps.  `bn` is the MMA's column count per tile, `slices` the number of K slices.  Without `swap`,
     256-wide tiles and one slice run as the persistent kernel (one CTA per SM walks the tiles) unless
@@ -854,7 +856,9 @@ def gemm_tc(x, w, out, bias=None, n_rows=None, swiglu=False, swap=None, bn=None,
     if swiglu:
         _need(N % 16 == 0 and out.dtype == torch.bfloat16 and out.shape[-1] == N // 2,
               "gemm_tc swiglu: w [2F,K] with F a multiple of 8, out bfloat16 [M,F]")
-        epi = 2
+        epi = 2 + GATE_ACTIVATIONS[activation]
+        _need(epi == 2 or (not swap and bn == 256 and slices in (None, 1) and persistent),
+              "gemm_tc: gates with another activation than SiLU run in the persistent forms only")
     else:
         _need(out.shape[-1] == N and out.dtype in (torch.bfloat16, torch.float32), "gemm_tc: out [M,N]")
         epi = 1 if out.dtype == torch.float32 else 0
@@ -1243,14 +1247,15 @@ ATTENTION_MAPS_MAX_DIM = 256
 
 
 def attention_prepare(buf, offsets, H, G, M, Dk, Dv, cache, ctx, q_weight=None, k_weight=None, eps=0.0, rot=None,
-                      write_cache=True):
+                      write_cache=True, bias=None):
     """Query and key norm, position rotation and the append of keys and values to the cache, for an attention
     whose heads have M score maps (csrc/attention_maps.cu).
 
     buf [T, N]: per token H*M query vectors of Dk at offsets[0], G*M key vectors of Dk at offsets[1], G value
     vectors of Dv at offsets[2] (which may be the keys' own place: values that are the keys as projected).
     The queries are rewritten in place; keys and values go to `cache` (a KVLayerView whose key pages are
-    [n_pages, G*M, page, Dk] and value pages [n_pages, G, page, Dv])."""
+    [n_pages, G*M, page, Dk] and value pages [n_pages, G, page, Dv]).  `bias` float32 [N]: the projection's
+    bias where the product left it out; it is added first."""
     k_pages, v_pages, table = cache.k, cache.v, cache.block_table
     cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
     _cuda(buf, k_pages, v_pages, table, q_weight, k_weight, cos, sin)
@@ -1279,12 +1284,17 @@ def attention_prepare(buf, offsets, H, G, M, Dk, Dv, cache, ctx, q_weight=None, 
               and 0 < n_rot <= Dk, "attention_prepare: rope tables float32 [P, n_rot/2], n_rot even and at most Dk")
         _need(ctx.max_kv_len <= cos.shape[0],
               f"rope tables hold {cos.shape[0]} positions, the step reaches position {ctx.max_kv_len}")
+    if bias is not None:
+        _cuda(bias)
+        _need(bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous(),
+              "attention_prepare: bias float32 [N]")
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.tok_seq, T, "tok_seq")
     _check(_lib("attention_maps").ab_attention_prepare(
         _p(buf), _dt(buf), N, off_q, off_k, off_v, H * M, G * M, G, Dk, Dv, _p(q_weight), _p(k_weight),
         ctypes.c_float(eps), _p(cos), _p(sin), n_rot, pairing, _p(ctx.tok_pos), _p(ctx.tok_seq), _p(table),
-        table.shape[1], _p(k_pages), _p(v_pages), page, T, 1 if write_cache else 0, _stream()), "attention_prepare")
+        table.shape[1], _p(k_pages), _p(v_pages), page, T, 1 if write_cache else 0, _p(bias), _stream()),
+        "attention_prepare")
 
 
 def attention_maps(q, q_stride, out, cache, ctx, H, G, M, Dk, Dv, scale, window=0, sink=None, coef=0.0,
@@ -1378,6 +1388,18 @@ def attention_maps_mma(q, q_stride, out, cache, ctx, H, G, M, Dk, Dv, scale, win
         return out
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+    if (USE_TCGEN05_ATTENTION and not ctx.is_decode and M == 1 and Dk == Dv and T >= 128 and q.shape[0] >= T
+            and q_stride % Dk == 0):
+        tc = _lib("attention_tc")
+        if tc.ab_attention_prefill_tc_supports(H, G, Dk):
+            # long prompts, one map, head size 64 or 128: the tcgen05 kernel (a sink in its last step)
+            _tc_unchecked["attention_tc"] = True
+            tile_seq, tile_q0, n_tiles, _ = _prefill_tiles(ctx, H // G, q.device, rows=128)
+            _check(tc.ab_attention_prefill_tc_sink(
+                _p(q), q_stride // Dk, T, _p(out), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(table), table.shape[1],
+                _p(ctx.tok_pos), _p(ctx.cu_q), _p(tile_seq), _p(tile_q0), n_tiles, H, G, Dk, ctypes.c_float(scale),
+                int(window or 0), _p(sink), _stream()), "attention_prefill_tc")
+            return out
     if ctx.is_decode:
         # one token per sequence: a tile per token; the rows are the batch rows themselves
         tile_seq = tile_q0 = _row_index(q.device, T)

@@ -7,11 +7,9 @@ one product feeds the activation kernel.  An inner width that is no multiple of
 weights are loaded: silu(0) * 0 adds nothing.
 
 The activation on the gate is SiLU unless another is named ("relu", "gelu_tanh": act(0) * 0 adds nothing
-either); those run the product and then the activation kernel, where SiLU has the fused forms.
+either); every form of the product applies the one that is named.
 """
 from __future__ import annotations
-
-import torch
 
 from .. import ops
 from .base import BuildOptions, FeedForward
@@ -34,14 +32,9 @@ class SwiGLU(FeedForward):
     adds_to_residual = True
 
     def accepts_owed_norm(self, n_rows: int) -> bool:
-        return self.activation == "silu" and self.gate_up.accepts_owed_norm(n_rows)
+        return self.gate_up.accepts_owed_norm(n_rows)
 
     def forward(self, h, ctx, then=None):
         T = ctx.n_tokens
-        if self.activation == "silu":
-            act = self.gate_up.forward_swiglu(h, n_rows=T)
-        else:
-            gu = self.gate_up.forward(h, n_rows=T)
-            act = torch.empty((gu.shape[0], self.gate_up.out_features // 2), dtype=gu.dtype, device=gu.device)
-            ops.gated_act(gu, act, self.activation, n_rows=T)
+        act = self.gate_up.forward_swiglu(h, n_rows=T, activation=self.activation)
         return self.down.forward(act, n_rows=T, then=then)

@@ -89,11 +89,12 @@ class Linear(Part):
         return (self.opts.dtype == torch.bfloat16 and self.weight is not None
                 and ops.owed_norm_pays(n_rows, self.out_features, self.in_features, self.weight.device))
 
-    def forward(self, x, n_rows: int | None = None, start_early: bool = True, then=None):
+    def forward(self, x, n_rows: int | None = None, start_early: bool = True, then=None, with_bias: bool = True):
         """`start_early` off: the product's kernel may not start before the kernel before it has ended
         (see `ops.gemv_bf16`).  `x` may be an `OwedNorm` (the division by the rms is applied to the
         sums).  `then` = (residual, norm): where the step has few enough rows, the result is added to
-        the residual here and an `OwedNorm` for `norm` is returned instead of the result."""
+        the residual here and an `OwedNorm` for `norm` is returned instead of the result.  `with_bias` off: the
+        caller adds `self.bias` itself (in a kernel that touches the result anyway)."""
         n = x.shape[0] if n_rows is None else n_rows
         owed = None
         if isinstance(x, OwedNorm):
@@ -108,23 +109,26 @@ class Linear(Part):
                                       owed=owed, residual=residual, norm_weight=d[0])
                 return OwedNorm(out, ss, d[1], d[2], norm)
         out = torch.empty((x.shape[0], self.out_features), dtype=self.out_dtype, device=x.device)
+        bias = self.bias if with_bias else None
         if x.dtype == torch.float32:
-            ops.gemm_f32(x, self.weight, out, bias=self.bias, n_rows=n)
+            ops.gemm_f32(x, self.weight, out, bias=bias, n_rows=n)
             return out
-        return ops.linear_bf16(x, self.weight, out, n_rows=n, bias=self.bias, start_early=start_early, owed=owed)
+        return ops.linear_bf16(x, self.weight, out, n_rows=n, bias=bias, start_early=start_early, owed=owed)
 
-    def forward_swiglu(self, x, n_rows: int | None = None) -> torch.Tensor:
-        """silu(gate) * up of the interleaved gate|up product, [M, out_features / 2]."""
+    def forward_swiglu(self, x, n_rows: int | None = None, activation: str = "silu") -> torch.Tensor:
+        """act(gate) * up of the interleaved gate|up product, [M, out_features / 2] (`activation`: "silu",
+        "relu" or "gelu_tanh" on the gate)."""
         n = x.shape[0] if n_rows is None else n_rows
         if isinstance(x, OwedNorm):
             act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
             return ops.gemv_bf16(x.x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True,
-                                 owed=(x.ss, x.width, x.eps))
+                                 owed=(x.ss, x.width, x.eps), activation=activation)
         act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
         if x.dtype == torch.bfloat16 and self.in_features % 8 == 0:
             if n <= ops.GEMV_MAX_ROWS:
-                return ops.gemv_bf16(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True)
+                return ops.gemv_bf16(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True, activation=activation)
             if n >= ops.TC_PERSISTENT_MIN_ROWS:
                 # long prompts: the persistent tcgen05 product with the activation in its tail
-                return ops.gemm_tc(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True, swap=False)
-        return ops.swiglu(self.forward(x, n_rows=n), act, n_rows=n)
+                return ops.gemm_tc(x, self.weight, act, bias=self.bias, n_rows=n, swiglu=True, swap=False,
+                                   activation=activation)
+        return ops.gated_act(self.forward(x, n_rows=n), act, activation, n_rows=n)

@@ -104,11 +104,14 @@ class MapsAttention(Mixer):
 
     def forward(self, h, ctx, cache, write_cache: bool = True):
         T = ctx.n_tokens
-        buf = self.qkv.forward(h, n_rows=T)
+        # many rows in bfloat16: the library product has no bias in it, and the kernel that prepares q and k
+        # touches every projected value anyway; few rows and the 32-bit path add it in the product
+        later = self.qkv.bias is not None and h.dtype == torch.bfloat16 and T > ops.GEMV_NARROW_MAX_ROWS
+        buf = self.qkv.forward(h, n_rows=T, with_bias=not later)
         rot = self.position.rotation() if self.position is not None else None
         ops.attention_prepare(buf, self.offsets, self.H, self.G, self.M, self.Dk, self.Dv, cache, ctx,
                               q_weight=self.q_weight, k_weight=self.k_weight, eps=self.eps, rot=rot,
-                              write_cache=write_cache)
+                              write_cache=write_cache, bias=self.qkv.bias if later else None)
         att = torch.empty((buf.shape[0], self.H * self.Dv), dtype=buf.dtype, device=buf.device)
         unit = self.difference is not None
         attend = ops.attention_maps_mma if self._on_tensor_cores(buf) else ops.attention_maps

@@ -126,6 +126,10 @@ SHAPES = [
     ("keys", 2, 2, 32, None, 33, {"base": 300.0, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}),
     ("keys", 6, 2, 48, None, 64, {"base": 20000.0, "dims": 16}),
     ("keys", 2, 1, 144, None, 63, {"base": 20000.0, "dims": 100}),
+    # head sizes 64 and 128: prompts of 128 tokens and more take the tcgen05 kernel in bfloat16
+    ("keys", 4, 2, 64, None, 100, {"base": 20000.0, "dims": 32}),
+    ("keys", 2, 1, 128, None, 70, {"base": 1000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}),
+    ("diff", 4, 2, 64, 128, 100, {"base": 500000.0, "dims": 32, "scaling": {"factor": 4.0}}),
 ]
 
 
