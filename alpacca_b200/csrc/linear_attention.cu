@@ -16,7 +16,10 @@
 //   stream   (prompts) a kernel first applies the activation to q | k | v in place; then one CTA per (sequence,
 //            head, 8 or 32 columns) with a column spread over 16 or 4 threads, and the activated rows of 8 or 16
 //            tokens at a time arriving in shared memory by cp.async, two buffers, so that the walk does not
-//            wait for memory and one sequence spreads over many processors.
+//            wait for memory and one sequence spreads over many processors.  Few long sequences are cut into
+//            pieces that are walked side by side: first every piece alone from a zero state (no outputs), which
+//            leaves its own sum U_p; then S_p = a^len_p S_{p-1} + U_p along each sequence gives the state before
+//            every piece; then every piece again from that state, with outputs.
 // The state of a sequence is read when the step starts and written back when it ends, so a prompt may be cut
 // anywhere and a decode step is the same code with one token.  The projections come as one float32 row per
 // token: zq | zk | zv | g at given offsets.
@@ -34,6 +37,12 @@ struct LinAttnArgs {
   const int* tok_seq;      // [T], -1: a row without a sequence
   float* o_raw;            // [T, H, V]
   int write_state;
+  // the stream form on pieces of sequences (mode 1, 2); mode 0 walks whole sequences from state to state
+  int mode;                // 1: a piece from zero, its sum to `pieces`, no outputs; 2: a piece from pieces[item], outputs
+  const int* item_seq;     // [n_items] the sequence of each piece
+  const int* item_t0;      // [n_items] its first packed token
+  const int* item_t1;      // [n_items] one past its last
+  float* pieces;           // [n_items, H, D, V]
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -149,19 +158,23 @@ linattn_stream_kernel(LinAttnArgs a) {
   float* part = vs + 2 * TB * COLS;           // [TB][SL][COLS]
   pdl_wait();
   pdl_trigger();
-  const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
-  const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
+  const int h = blockIdx.y, c0 = blockIdx.z * COLS;
+  const int b = a.mode == 0 ? (int)blockIdx.x : a.item_seq[blockIdx.x];
+  const int t0 = a.mode == 0 ? a.cu_q[b] : a.item_t0[blockIdx.x];
+  const int t1 = a.mode == 0 ? a.cu_q[b + 1] : a.item_t1[blockIdx.x];
   const int slot = a.slots[b];
   if (slot < 0 || t1 <= t0 || a.tok_seq[t0] < 0) return;
   const int tid = threadIdx.x, c = tid % COLS, r = tid / COLS;
   const int D = a.D, V = a.V, col = c0 + c;
   const float lam = a.decay[h];
-  float* st = a.state + ((size_t)slot * a.H + h) * (size_t)D * V;
+  const bool outputs = a.mode != 1;
+  float* st = a.mode == 0 ? a.state + ((size_t)slot * a.H + h) * (size_t)D * V
+                          : a.pieces + ((size_t)blockIdx.x * a.H + h) * (size_t)D * V;
   float s[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
     const int d = r * DPT + i;
-    s[i] = (d < D && col < V) ? st[(size_t)d * V + col] : 0.f;
+    s[i] = (a.mode != 1 && d < D && col < V) ? st[(size_t)d * V + col] : 0.f;
   }
   // rows of S past D meet zeros: the padding of both buffers is cleared once and never written again
   for (int i = tid; i < 2 * TB * DP; i += 128) { qs[i] = 0.f; ks[i] = 0.f; }
@@ -173,7 +186,7 @@ linattn_stream_kernel(LinAttnArgs a) {
     for (int i = tid; i < n * d4; i += 128) {
       const int tok = i / d4, piece = i - tok * d4;
       const float* row = a.proj + (size_t)(tb + tok) * a.ld + h * D + piece * 4;
-      la_cp_async_16(qs + (stage * TB + tok) * DP + piece * 4, row + a.off_q);
+      if (outputs) la_cp_async_16(qs + (stage * TB + tok) * DP + piece * 4, row + a.off_q);
       la_cp_async_16(ks + (stage * TB + tok) * DP + piece * 4, row + a.off_k);
     }
     for (int i = tid; i < n * COLS; i += 128) {
@@ -190,6 +203,21 @@ linattn_stream_kernel(LinAttnArgs a) {
     __syncthreads();
     const float* qb = qs + stage * TB * DP + r * DPT;
     const float* kb = ks + stage * TB * DP + r * DPT;
+    if (!outputs) {
+      for (int tok = 0; tok < n; ++tok) {
+        const float vv = vs[(stage * TB + tok) * COLS + c];
+#pragma unroll
+        for (int i = 0; i < DPT; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kb + tok * DP + i);
+          s[i] = fmaf(lam, s[i], k4.x * vv);
+          s[i + 1] = fmaf(lam, s[i + 1], k4.y * vv);
+          s[i + 2] = fmaf(lam, s[i + 2], k4.z * vv);
+          s[i + 3] = fmaf(lam, s[i + 3], k4.w * vv);
+        }
+      }
+      __syncthreads();
+      continue;
+    }
     for (int tok = 0; tok < n; ++tok) {
       const float vv = vs[(stage * TB + tok) * COLS + c];
       float acc0 = 0.f, acc1 = 0.f;
@@ -220,13 +248,43 @@ linattn_stream_kernel(LinAttnArgs a) {
     }
     // the next round's first barrier comes before `part` and this stage's buffers are written again
   }
-  if (a.write_state && col < V) {
+  if ((a.mode == 0 ? a.write_state : (a.mode == 1)) && col < V) {
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
       const int d = r * DPT + i;
       if (d < D) st[(size_t)d * V + col] = s[i];
     }
   }
+}
+
+// Along each sequence: pieces[p] <- the state before piece p, and the state moves on by a^len_p S + U_p; at the
+// end it is the sequence's new state.  A thread per element of S.
+__global__ void linattn_combine_kernel(LinAttnArgs a, const int* __restrict__ seq_first, const int* __restrict__ seq_count,
+                                       int n_seqs) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t per_head = (size_t)a.D * a.V, per_seq = per_head * a.H;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= per_seq * n_seqs) return;
+  const int b = (int)(i / per_seq);
+  const size_t e = i - (size_t)b * per_seq;
+  const int h = (int)(e / per_head);
+  const int slot = a.slots[b], n = seq_count[b], first = seq_first[b];
+  if (slot < 0 || n <= 0 || a.tok_seq[a.item_t0[first]] < 0) return;
+  const float lam = a.decay[h];
+  float* st = a.state + (size_t)slot * per_seq + e;
+  float S = *st;
+  int len_known = -1;
+  float pw = 1.f;
+  for (int p = first; p < first + n; ++p) {
+    const int len = a.item_t1[p] - a.item_t0[p];
+    if (len != len_known) { pw = powf(lam, (float)len); len_known = len; }
+    float* u = a.pieces + (size_t)p * per_seq + e;
+    const float U = *u;
+    *u = S;
+    S = fmaf(pw, S, U);
+  }
+  if (a.write_state) *st = S;
 }
 
 template <int DPT, int SL, int TB>
@@ -243,6 +301,22 @@ static int launch_stream(const LinAttnArgs& a, int n_seqs, cudaStream_t stream) 
   ab_launch(linattn_stream_kernel<DPT, SL, TB>, dim3((unsigned)n_seqs, (unsigned)a.H, col_tiles), dim3(128), smem, stream, a);
   return ab_launch_status();
 }
+
+// the stream kernel's form for D; `rows`: sequences (mode 0) or pieces
+static int stream_dispatch(const LinAttnArgs& a, int rows, cudaStream_t stream) {
+  const int D = a.D;
+  if (D % 64 == 0 && D <= 64) return launch_stream<4, 16, 16>(a, rows, stream);
+  if (D % 64 == 0 && D <= 128) return launch_stream<8, 16, 16>(a, rows, stream);
+  if (D % 64 == 0) return launch_stream<16, 16, 8>(a, rows, stream);
+  if (D <= 16) return launch_stream<4, 4, 16>(a, rows, stream);
+  if (D <= 32) return launch_stream<8, 4, 16>(a, rows, stream);
+  if (D <= 64) return launch_stream<16, 4, 16>(a, rows, stream);
+  if (D <= 128) return launch_stream<32, 4, 16>(a, rows, stream);
+  return launch_stream<64, 4, 8>(a, rows, stream);
+}
+
+// columns of S per CTA of the stream form (its callers plan their pieces by the number of CTAs)
+AB_API int ab_linear_attention_stream_cols(int D) { return D % 64 == 0 ? 8 : 32; }
 
 // out[t, j] = o[t, j] / rms(o[t, :]) * weight[j] * sigmoid(g[t, j]) over all H*V values of a token; a block per token
 template <typename T>
@@ -334,15 +408,21 @@ __global__ void linattn_activate4_kernel(float* __restrict__ proj, int ld, int c
 AB_API int ab_linear_attention_max_dim() { return 64 * LA_SLICES; }
 
 // `stream_from`: steps with more than this many tokens per sequence on average take the `stream` form (it rewrites
-// q | k | v of `proj` in place with their activations).
+// q | k | v of `proj` in place with their activations).  With n_items > 0 the stream form walks pieces of the
+// sequences side by side: piece p is the packed tokens item_t0[p] .. item_t1[p] - 1 of sequence item_seq[p]; the pieces
+// of sequence b are seq_first[b] .. seq_first[b] + seq_count[b] - 1, in order, and cover its tokens; `pieces` is
+// scratch, float [n_items, H, D, V].
 AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int off_k, int off_v, int off_g,
                                     const float* decay, float* state, int H, int D, int V, const int* cu_q,
                                     const int* slots, const int* tok_seq, int n_seqs, int n_tokens, float* o_raw,
                                     const float* weight, float eps, void* out, int out_dtype, int write_state,
-                                    int stream_from, cudaStream_t stream) {
+                                    int stream_from, const int* item_seq, const int* item_t0, const int* item_t1,
+                                    int n_items, float* pieces, const int* seq_first, const int* seq_count,
+                                    cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return AB_OK;
   if (H <= 0 || D <= 0 || V <= 0 || D > 64 * LA_SLICES || H > 65535) return AB_BAD_ARG;
-  LinAttnArgs a{proj, ld, off_q, off_k, off_v, off_g, decay, state, H, D, V, cu_q, slots, tok_seq, o_raw, write_state};
+  LinAttnArgs a{proj, ld, off_q, off_k, off_v, off_g, decay, state, H, D, V, cu_q, slots, tok_seq, o_raw, write_state,
+                0, nullptr, nullptr, nullptr, nullptr};
   const unsigned col_tiles = (unsigned)((V + LA_COLS - 1) / LA_COLS);
   if (col_tiles > 65535) return AB_BAD_ARG;
   int rc;
@@ -360,14 +440,22 @@ AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int of
                 const_cast<float*>(proj), ld, c0, c1, tok_seq, n_tokens);
     rc = ab_launch_status();
     if (rc) return rc;
-    if (D % 64 == 0 && D <= 64) rc = launch_stream<4, 16, 16>(a, n_seqs, stream);
-    else if (D % 64 == 0 && D <= 128) rc = launch_stream<8, 16, 16>(a, n_seqs, stream);
-    else if (D % 64 == 0) rc = launch_stream<16, 16, 8>(a, n_seqs, stream);
-    else if (D <= 16) rc = launch_stream<4, 4, 16>(a, n_seqs, stream);
-    else if (D <= 32) rc = launch_stream<8, 4, 16>(a, n_seqs, stream);
-    else if (D <= 64) rc = launch_stream<16, 4, 16>(a, n_seqs, stream);
-    else if (D <= 128) rc = launch_stream<32, 4, 16>(a, n_seqs, stream);
-    else rc = launch_stream<64, 4, 8>(a, n_seqs, stream);
+    if (n_items > 0) {
+      if (!item_seq || !item_t0 || !item_t1 || !pieces || !seq_first || !seq_count) return AB_BAD_ARG;
+      a.item_seq = item_seq; a.item_t0 = item_t0; a.item_t1 = item_t1; a.pieces = pieces;
+      a.mode = 1;
+      rc = stream_dispatch(a, n_items, stream);
+      if (rc) return rc;
+      const size_t elems = (size_t)n_seqs * H * D * V;
+      ab_launch(linattn_combine_kernel, dim3((unsigned)((elems + 255) / 256)), dim3(256), 0, stream, a, seq_first, seq_count,
+                n_seqs);
+      rc = ab_launch_status();
+      if (rc) return rc;
+      a.mode = 2;
+      rc = stream_dispatch(a, n_items, stream);
+    } else {
+      rc = stream_dispatch(a, n_seqs, stream);
+    }
   } else {
     dim3 grid((unsigned)n_seqs, (unsigned)H, col_tiles), block(LA_COLS * LA_SLICES);
     const int dpt = (D + LA_SLICES - 1) / LA_SLICES;

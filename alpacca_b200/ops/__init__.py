@@ -1203,6 +1203,42 @@ def linear_attention_max_dim() -> int:
 
 
 LINEAR_ATTENTION_STREAM_FROM = 32     # tokens per sequence (on average) from which a step takes the form for prompts
+LINEAR_ATTENTION_PIECES = True        # few long sequences are cut into pieces that are walked side by side
+LINEAR_ATTENTION_CTAS = 2048          # ... as many as give about this many CTAs, none shorter than 64 tokens
+
+
+def _linear_attention_pieces(ctx, H, D, V, device):
+    """The pieces of a prompt step for the linear attention's walk, or None where the sequences alone fill the
+    device: (item_seq, item_t0, item_t1, n_items, seq_first, seq_count) as device arrays, planned once per step
+    from the lengths (which belong to the shape of a captured step)."""
+    if not LINEAR_ATTENTION_PIECES or ctx.host_q_lens is None:
+        return None
+    cols = _lib("linear_attention").ab_linear_attention_stream_cols(D)
+    per_seq = H * -(-V // cols)
+    want = -(-LINEAR_ATTENTION_CTAS // max(per_seq * ctx.n_seqs, 1))
+    if want <= 1:
+        return None
+    piece = max(64, -(-(-(-max(ctx.host_q_lens) // want)) // 16) * 16)
+    if max(ctx.host_q_lens) < 2 * piece:
+        return None
+    key = ("linear_attention_pieces", piece)
+    plan = ctx.extras.get(key)
+    if plan is None:
+        seq, t0, t1, first, count, start = [], [], [], [], [], 0
+        for b, q in enumerate(ctx.host_q_lens):
+            first.append(len(seq))
+            for at in range(0, q, piece):
+                seq.append(b)
+                t0.append(start + at)
+                t1.append(start + min(at + piece, q))
+            count.append(len(seq) - first[-1])
+            start += q
+        n = len(seq)
+        flat = torch.tensor(seq + t0 + t1 + first + count, dtype=torch.int32).to(device)
+        B = ctx.n_seqs
+        plan = (flat[:n], flat[n:2 * n], flat[2 * n:3 * n], n, flat[3 * n:3 * n + B], flat[3 * n + B:3 * n + 2 * B])
+        ctx.extras[key] = plan
+    return plan
 
 
 def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight, eps, out, write_state=True):
@@ -1235,11 +1271,16 @@ def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight
     _i32(ctx.slots, B, "slots")
     _i32(ctx.tok_seq, T, "tok_seq")
     o_raw = torch.empty((T, H * V), dtype=torch.float32, device=proj.device)
+    long_step = T > LINEAR_ATTENTION_STREAM_FROM * B
+    plan = _linear_attention_pieces(ctx, H, D, V, proj.device) if long_step else None
+    item_seq, item_t0, item_t1, n_items, seq_first, seq_count = plan if plan is not None else (None,) * 3 + (0, None, None)
+    pieces = torch.empty((n_items, H, D, V), dtype=torch.float32, device=proj.device) if n_items else None
     _check(_lib("linear_attention").ab_linear_attention_step(
         _p(proj), ld, off_q, off_k, off_v, off_g, _p(decay), _p(state), H, D, V, _p(ctx.cu_q), _p(ctx.slots),
         _p(ctx.tok_seq), B, T, _p(o_raw), _p(norm_weight), ctypes.c_float(eps), _p(out), _dt(out),
-        1 if write_state else 0, LINEAR_ATTENTION_STREAM_FROM, _stream()), "linear_attention_step",
-        kernels=3 if T > LINEAR_ATTENTION_STREAM_FROM * B else 2)
+        1 if write_state else 0, LINEAR_ATTENTION_STREAM_FROM, _p(item_seq), _p(item_t0), _p(item_t1), n_items,
+        _p(pieces), _p(seq_first), _p(seq_count), _stream()), "linear_attention_step",
+        kernels=(5 if n_items else 3) if long_step else 2)
     return out
 
 
@@ -1388,8 +1429,8 @@ def attention_maps_mma(q, q_stride, out, cache, ctx, H, G, M, Dk, Dv, scale, win
         return out
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
-    if (USE_TCGEN05_ATTENTION and not ctx.is_decode and M == 1 and Dk == Dv and T >= 128 and q.shape[0] >= T
-            and q_stride % Dk == 0):
+    if (USE_TCGEN05_ATTENTION and not ctx.is_decode and M == 1 and Dk == Dv and Dk in (64, 128) and T >= 128
+            and q.shape[0] >= T and q_stride % Dk == 0):
         tc = _lib("attention_tc")
         if tc.ab_attention_prefill_tc_supports(H, G, Dk):
             # long prompts, one map, head size 64 or 128: the tcgen05 kernel (a sink in its last step)

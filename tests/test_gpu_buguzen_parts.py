@@ -90,6 +90,12 @@ def test_linear_attention(dtype, H, D, V, decay):
     s2 = hs.cache.alloc_slot()
     assert s2 == s0
     close(feed(part, hs, s2, xs[1][0], (31,)), want[1], dtype, "linear attention, a slot used again")
+    # a long prompt in one step is cut into pieces that are walked side by side; the state they leave is the one
+    # that the next portion starts from
+    long_x, long64 = hidden(rng, 330, width, dtype)
+    s3 = hs.cache.alloc_slot()
+    close(feed(part, hs, s3, long_x, (300, 30)), plain.lightning(long64, w, mx, eps)[0], dtype,
+          "linear attention, a long prompt in pieces")
     state = hs.cache.entry_view(0, None).state[s2].double().cpu().numpy()
     close(state, plain.lightning(xs[1][1], w, mx, eps)[1], dtype, "linear attention, the state", tol=(0.05, 0.01) if dtype == "bfloat16" else None)
 
