@@ -134,9 +134,29 @@ __global__ void stream_cast_bf16x4_kernel(float* __restrict__ x, const bf16* __r
   reinterpret_cast<uint2*>(y)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
 }
 
+// four columns per thread (width a multiple of 4)
+__global__ void add_row4_kernel(float* __restrict__ x, const float* __restrict__ row, const int* __restrict__ tok_seq,
+                                size_t total4, int width4) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total4) return;
+  const size_t t = i / width4;
+  if (tok_seq[t] < 0) return;
+  const float4 r = reinterpret_cast<const float4*>(row)[i - t * width4];
+  float4 v = reinterpret_cast<float4*>(x)[i];
+  v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+  reinterpret_cast<float4*>(x)[i] = v;
+}
+
 AB_API int ab_add_row(float* x, const float* row, const int* tok_seq, int n_rows, int width, cudaStream_t stream) {
   const size_t total = (size_t)n_rows * width;
   if (total == 0) return AB_OK;
+  if (width % 4 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    ab_launch(add_row4_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, x, row, tok_seq, total / 4,
+              width / 4);
+    return ab_launch_status();
+  }
   ab_launch(add_row_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, row, tok_seq, total, width);
   return ab_launch_status();
 }
