@@ -289,6 +289,49 @@ __global__ void linattn_combine_kernel(LinAttnArgs a, const int* __restrict__ se
   if (a.write_state) *st = S;
 }
 
+// The same, four elements per thread (D * V a multiple of 4) and the pieces' sums of four pieces fetched before any of
+// them is overwritten, so that a thread's loads do not wait for one another.
+__global__ void linattn_combine4_kernel(LinAttnArgs a, const int* __restrict__ seq_first, const int* __restrict__ seq_count,
+                                        int n_seqs) {
+  pdl_wait();
+  pdl_trigger();
+  const unsigned per_head4 = (unsigned)(a.D * a.V) >> 2, per_seq4 = per_head4 * a.H;
+  const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= per_seq4 * (unsigned)n_seqs) return;
+  const int b = (int)(i / per_seq4);
+  const unsigned e = i - (unsigned)b * per_seq4;
+  const int h = (int)(e / per_head4);
+  const int slot = a.slots[b], n = seq_count[b], first = seq_first[b];
+  if (slot < 0 || n <= 0 || a.tok_seq[a.item_t0[first]] < 0) return;
+  const float lam = a.decay[h], l2 = lam >= 1.f ? 0.f : log2f(lam);
+  float4* st = reinterpret_cast<float4*>(a.state) + (size_t)slot * per_seq4 + e;
+  float4* pieces = reinterpret_cast<float4*>(a.pieces) + e;
+  float4 S = *st;
+  for (int p0 = first; p0 < first + n; p0 += 4) {
+    const int m = min(4, first + n - p0);
+    float4 U[4];
+    float pw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j < m) {
+        U[j] = pieces[(size_t)(p0 + j) * per_seq4];
+        pw[j] = exp2f((float)(a.item_t1[p0 + j] - a.item_t0[p0 + j]) * l2);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j < m) {
+        pieces[(size_t)(p0 + j) * per_seq4] = S;
+        S.x = fmaf(pw[j], S.x, U[j].x);
+        S.y = fmaf(pw[j], S.y, U[j].y);
+        S.z = fmaf(pw[j], S.z, U[j].z);
+        S.w = fmaf(pw[j], S.w, U[j].w);
+      }
+    }
+  }
+  if (a.write_state) *st = S;
+}
+
 template <int DPT, int SL, int TB>
 static int launch_stream(const LinAttnArgs& a, int n_seqs, cudaStream_t stream) {
   constexpr int COLS = 128 / SL, DP = DPT * SL;
@@ -449,8 +492,12 @@ AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int of
       rc = stream_dispatch(a, n_items, stream);
       if (rc) return rc;
       const size_t elems = (size_t)n_seqs * H * D * V;
-      ab_launch(linattn_combine_kernel, dim3((unsigned)((elems + 255) / 256)), dim3(256), 0, stream, a, seq_first, seq_count,
-                n_seqs);
+      if ((D * V) % 4 == 0 && elems / 4 < 0x7fffffffULL)
+        ab_launch(linattn_combine4_kernel, dim3((unsigned)((elems / 4 + 255) / 256)), dim3(256), 0, stream, a, seq_first,
+                  seq_count, n_seqs);
+      else
+        ab_launch(linattn_combine_kernel, dim3((unsigned)((elems + 255) / 256)), dim3(256), 0, stream, a, seq_first,
+                  seq_count, n_seqs);
       rc = ab_launch_status();
       if (rc) return rc;
       a.mode = 2;
