@@ -587,13 +587,13 @@ def _buguzen_config(z):
                  "mixer": {"heads": b["lin_heads"], "dim": b["lin_dim"], "vdim": b["lin_vdim"], "decay": _decays(b["lin_heads"])}}
     diff = {"type": "attention", "mlp": dense,
             "mixer": {"heads": b["diff_heads"], "kv_heads": z["kv_heads"], "dim": b["diff_dim"], "vdim": 2 * b["diff_dim"],
-                      "scale": b["diff_dim"] ** -0.5, "diff": 0.3, "mask": {"size": b["window"]},
-                      "rot": {"base": 500000.0, "dims": b["diff_dim"] // 2, "scaling": {"factor": 4.0}}}}
+                      "scale": b["diff_dim"] ** -0.5, "diff": 0.2, "mask": {"size": b["window"]},
+                      "rot": {"base": 100000.0, "dims": b["diff_dim"] // 2, "scaling": {"factor": 2.0}}}}
     keys = {"type": "attention_2", "mlp": dense,
             "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "scale": z["head_dim"] ** -0.5,
                       "mask": {"size": b["window"]},
-                      "rot": {"base": 1000000.0, "dims": z["head_dim"] // 2,
-                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}}
+                      "rot": {"base": 250000.0, "dims": z["head_dim"] // 2,
+                              "scaling": {"factor": 16.0, "low": 1.0, "high": 8.0, "original": 2048}}}}
     return {"architecture": "Buguzen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
             "layers": [lightning, diff, keys, lightning, diff, keys], "loop": {"start": 2, "stop": 4, "times": 2},
             "token_side": {"dim": b["side"]}}

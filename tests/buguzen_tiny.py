@@ -57,7 +57,7 @@ TINY_W = {
     "architecture": "Buguzen", "vocab": 67, "width": 64, "norm": {"eps": 1e-6},
     "layers": [
         {"type": "lightning", "mixer": _lightning(1, 40, 36, (0.97,)), "mlp": {"kind": "dense", "ff": 48}},
-        {"type": "attention_2", "mixer": _keyval(2, 2, 32, 33, 0.2, 300.0, 32, (8.0, 1.0, 4.0, 64)), "mlp": None},
+        {"type": "attention_2", "mixer": _keyval(2, 2, 32, 33, 0.2, 300.0, 32, (6.0, 1.0, 4.0, 64)), "mlp": None},
         {"type": "attention", "mixer": _diff(2, 1, 32, 16, 130, 0.18, 0.4, 50000.0, 32), "mlp": {"kind": "dense", "ff": 80}},
         {"type": "lightning", "mixer": _lightning(2, 16, 72, (0.8, 0.999)), "mlp": None},
     ],

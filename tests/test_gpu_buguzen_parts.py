@@ -100,7 +100,7 @@ def test_linear_attention(dtype, H, D, V, decay):
     close(state, plain.lightning(xs[1][1], w, mx, eps)[1], dtype, "linear attention, the state", tol=(0.05, 0.01) if dtype == "bfloat16" else None)
 
 
-def attention_part(dtype, kind, width, H, G, D, V, window, rot, scale, eps, diff=0.3):
+def attention_part(dtype, kind, width, H, G, D, V, window, rot, scale, eps, diff=0.35):
     from alpacca_b200.parts import MapsAttention, RotaryEncoding
     sc = rot.get("scaling")
     scaling = None
@@ -129,13 +129,13 @@ SHAPES = [
     ("diff", 3, 3, 20, 20, 64, {"base": 100.0, "dims": 10, "scaling": {"factor": 3.0}}),
     ("diff", 1, 1, 72, 136, 65, {"base": 1000.0, "dims": 72}),
     ("keys", 4, 1, 20, None, 70, {"base": 5000.0, "dims": 12, "scaling": {"factor": 4.0, "low": 1.0, "high": 3.0, "original": 48}}),
-    ("keys", 2, 2, 32, None, 33, {"base": 300.0, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}),
+    ("keys", 2, 2, 32, None, 33, {"base": 300.0, "dims": 32, "scaling": {"factor": 5.0, "low": 1.0, "high": 4.0, "original": 64}}),
     ("keys", 6, 2, 48, None, 64, {"base": 20000.0, "dims": 16}),
     ("keys", 2, 1, 144, None, 63, {"base": 20000.0, "dims": 100}),
     # head sizes 64 and 128: prompts of 128 tokens and more take the tcgen05 kernel in bfloat16
     ("keys", 4, 2, 64, None, 100, {"base": 20000.0, "dims": 32}),
-    ("keys", 2, 1, 128, None, 70, {"base": 1000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}),
-    ("diff", 4, 2, 64, 128, 100, {"base": 500000.0, "dims": 32, "scaling": {"factor": 4.0}}),
+    ("keys", 2, 1, 128, None, 70, {"base": 1000.0, "dims": 64, "scaling": {"factor": 6.0, "low": 1.0, "high": 3.0, "original": 64}}),
+    ("diff", 4, 2, 64, 128, 100, {"base": 200000.0, "dims": 32, "scaling": {"factor": 3.0}}),
 ]
 
 
@@ -179,8 +179,10 @@ def test_attention_whole_portions_and_single_tokens(dtype, kind, H, G, D, V, win
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kind,window,D,V", [("diff", 40, 16, 24), ("diff", 64, 32, 16), ("diff", 100, 24, 40),
-                                             ("keys", 40, 32, None), ("keys", 64, 20, None), ("keys", 129, 48, None)])
+@pytest.mark.parametrize("kind,window,D,V", [("diff", 33, 16, 24), ("diff", 64, 32, 16), ("diff", 100, 24, 40),
+                                             ("keys", 33, 32, None), ("keys", 64, 20, None), ("keys", 129, 48, None),
+                                             # a key among six hundred, nine pages back
+                                             ("diff", 600, 32, 48), ("keys", 600, 64, None)])
 @pytest.mark.parametrize("decode", [False, True])
 def test_a_key_just_inside_and_just_outside_the_window(dtype, kind, window, D, V, decode):
     """One early token carries a value that no other has, and queries that look for it.  With scores made so
