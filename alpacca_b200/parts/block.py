@@ -30,7 +30,8 @@ class HiddenStream:
 class PreNormBlock(Block):
     """`after`: a part that acts on the stream once the sub-layers are done (`forward(stream, ctx)`; a layer's
     token input, say).  It reads the stream as it stands, so the last sub-layer's output is not prepared
-    for the next block's norm then."""
+    for the next block's norm then; if the part has a `cast` (a norm-like stand-in for "the stream in the
+    activation dtype"), the last sub-layer may prepare that instead."""
 
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None, ffn: FeedForward | None, after=None):
         self.norm1, self.mixer, self.norm2, self.ffn, self.after = norm1, mixer, norm2, ffn, after
@@ -45,7 +46,7 @@ class PreNormBlock(Block):
     def forward(self, stream: HiddenStream, ctx, cache, write_cache: bool = True) -> None:
         next_norm, stream.next_norm = stream.next_norm, None
         if self.after is not None:
-            next_norm = None
+            next_norm = getattr(self.after, "cast", None)
         h = _normed(self.norm1, stream)
         if self.ffn is None:
             _sublayer(stream, next_norm, self.mixer, h, ctx, cache, write_cache)

@@ -59,10 +59,12 @@ class DecayLinearAttention(Mixer):
     def cache_spec(self):
         return StateSpec((self.H, self.D, self.V), torch.float32)
 
-    def forward(self, h, ctx, cache, write_cache: bool = True):
+    adds_to_residual = True
+
+    def forward(self, h, ctx, cache, write_cache: bool = True, then=None):
         T = ctx.n_tokens
         proj = self.proj.forward(h, n_rows=T)
         mixed = torch.empty((proj.shape[0], self.H * self.V), dtype=self.opts.dtype, device=proj.device)
         ops.linear_attention_step(proj, self.offsets, self.decay, cache.state, ctx, self.H, self.D, self.V,
                                   self.norm_weight, self.eps, mixed, write_state=write_cache)
-        return self.out.forward(mixed, n_rows=T)
+        return self.out.forward(mixed, n_rows=T, then=then)

@@ -102,7 +102,9 @@ class MapsAttention(Mixer):
     def _on_tensor_cores(self, buf) -> bool:
         return ops.attention_maps_mma_supports(self.H, self.G, self.M, self.Dk, self.Dv, buf.shape[-1], buf.dtype)
 
-    def forward(self, h, ctx, cache, write_cache: bool = True):
+    adds_to_residual = True
+
+    def forward(self, h, ctx, cache, write_cache: bool = True, then=None):
         T = ctx.n_tokens
         # many rows in bfloat16: the library product has no bias in it, and the kernel that prepares q and k
         # touches every projected value anyway; few rows and the 32-bit path add it in the product
@@ -119,4 +121,4 @@ class MapsAttention(Mixer):
                self.window or 0, self.sink, coef=self.coef, unit_norm=unit, eps=self.eps,
                out_scale=(1.0 - self.difference) if unit else 1.0)
         # after a kernel that fills the processors' shared memory the product starts when that kernel has ended
-        return self.out.forward(att, n_rows=T, start_early=False)
+        return self.out.forward(att, n_rows=T, start_early=False, then=then)

@@ -7,6 +7,10 @@
                    e = table[token][i*dim:(i+1)*dim];  a = gelu_tanh(W_gate x) * e;  y = W_proj a
                    x <- x + y / sqrt(mean(y^2) + eps) * w
                x is the stream as it stands (no norm before W_gate); the norm of y is 32-bit.
+`StreamCast`   stands where a part reads the stream itself in the activation dtype.  To the block it is a norm whose
+               weight is 1 and whose division nobody owes: in a step of a few rows the product before it adds its
+               result to the stream and leaves bf16(stream) behind (the skinny product's residual tail), and the
+               kernel that casts the stream is not launched.
 """
 from __future__ import annotations
 
@@ -14,8 +18,27 @@ import torch
 
 from .. import ops
 from ..weights.loader import ParamSpec
-from .base import BuildOptions, Part
+from .base import BuildOptions, Norm, Part
 from .linear import Linear
+
+
+class StreamCast(Norm):
+    def __init__(self, opts: BuildOptions, width: int):
+        self.opts, self.width = opts, int(width)
+        self.ones = torch.ones(self.width, dtype=torch.float32, device=opts.device)
+
+    def deferred(self):
+        if self.opts.dtype != torch.bfloat16:
+            return None
+        return self.ones, self.width, 0.0
+
+    def forward(self, residual, delta, out=None, rows=None, n_rows=None):
+        """residual += delta; the stream in the activation dtype."""
+        if rows is not None:
+            raise ValueError("the cast stream is read in full")
+        if out is None:
+            out = torch.empty(residual.shape, dtype=self.opts.dtype, device=residual.device)
+        return ops.stream_cast(residual, delta, out, n_rows=n_rows)
 
 
 class PassOffset(Part):
@@ -56,6 +79,7 @@ class TokenSide(Part):
         if self.offset < 0 or self.offset + self.dim > table.columns:
             raise ValueError(f"{prefix}: columns {self.offset}..{self.offset + self.dim} lie outside the table's "
                              f"{table.columns}")
+        self.cast = StreamCast(opts, width)  # what the block may ask the part before this one to prepare
         self._table = {"part": table}       # shared by the layers and loaded once, by the model: not a child
         self.prefix, self.names = prefix, names
         gate, proj, _ = names
@@ -73,10 +97,12 @@ class TokenSide(Part):
     def forward(self, stream, ctx) -> None:
         T = ctx.n_tokens
         if stream.owed is not None:
-            raise RuntimeError("rows prepared for a norm cannot be read as the stream")
-        x = torch.empty(stream.residual.shape, dtype=self.opts.dtype, device=stream.residual.device)
-        ops.stream_cast(stream.residual, stream.delta, x, n_rows=T)
-        stream.delta = None
+            if stream.owed.norm is not self.cast:
+                raise RuntimeError("rows prepared for a norm cannot be read as the stream")
+            x, stream.owed = stream.owed.x, None      # the product before has added its result and left the cast
+        else:
+            x = self.cast.forward(stream.residual, stream.delta, n_rows=T)
+            stream.delta = None
         z = self.gate.forward(x, n_rows=T)
         a = torch.empty_like(z)
         ops.token_gate(z, self._table["part"].weight, self.offset, ctx, a)
