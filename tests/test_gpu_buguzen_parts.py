@@ -156,7 +156,7 @@ def test_attention_whole_portions_and_single_tokens(dtype, kind, H, G, D, V, win
     want, want_y = fn(x64, w, mx, eps), fn(y64, w, mx, eps)
     tol = TOL_DIFF_BF16 if (kind, dtype) == ("diff", "bfloat16") else None
     hs = PartHarness([part.cache_spec()], dtype, max_slots=4)
-    for cuts in ((150,), (2, 3, 59, 1, 64, 2, 19), (60,) + (1,) * 90):
+    for cuts in ((150,), (2, 3, 59, 1, 64, 2, 19), (20, 130), (60,) + (1,) * 90):
         s = hs.cache.alloc_slot()
         close(feed(part, hs, s, x, cuts), want, dtype, f"attention {kind} in portions {cuts[:4]}", tol=tol)
         hs.cache.free_slot(s)
