@@ -40,6 +40,11 @@ struct PrepareArgs {
   const float* bias;       // [stride] or null: added to the projected values first (a projection that left it out)
 };
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 attention_prepare_kernel(PrepareArgs a) {
@@ -107,6 +112,142 @@ attention_prepare_kernel(PrepareArgs a) {
     }
     dst[d] = from_f32<T>(v);
   }
+}
+
+// The same for bfloat16 rows in 16-byte pieces.  Query and key vectors: a lane owns 8 consecutive elements, a
+// vector takes P = Dk / 8 neighbouring lanes, a warp floor(32 / P) vectors (the norm's sum and the partner of a pair
+// in the other half come by shuffles inside the vector's lanes).  Value vectors: the warps after those, a lane per
+// piece.  Needs Dk, Dv, the offsets and the row stride to be multiples of 8, and for the pairing in halves n_rot a
+// multiple of 16 (a pair's two elements then sit at the same place of two pieces).
+__global__ void __launch_bounds__(128)
+attention_prepare_vec_kernel(PrepareArgs a, int P, int vec_per_warp, long long qk_warps) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (warp >= qk_warps) {
+    // value pieces: copied as projected (plus the bias)
+    if (!a.write_cache) return;
+    const int Pv = a.Dv >> 3;
+    const long long i = (warp - qk_warps) * 32 + lane;
+    if (i >= (long long)a.n_tokens * a.n_v * Pv) return;
+    const int t = (int)(i / (a.n_v * Pv));
+    const int rest = (int)(i - (long long)t * (a.n_v * Pv));
+    const int g = rest / Pv, piece = rest - g * Pv;
+    const int b = a.tok_seq[t];
+    if (b < 0) return;
+    const int pos = a.tok_pos[t];
+    const int col = a.off_v + g * a.Dv + piece * 8;
+    uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.buf) + (size_t)t * a.stride + col);
+    if (a.bias != nullptr) {
+      const float4 b0 = *reinterpret_cast<const float4*>(a.bias + col), b1 = *reinterpret_cast<const float4*>(a.bias + col + 4);
+      raw.x = pack2(__uint_as_float(raw.x << 16) + b0.x, __uint_as_float(raw.x & 0xffff0000u) + b0.y);
+      raw.y = pack2(__uint_as_float(raw.y << 16) + b0.z, __uint_as_float(raw.y & 0xffff0000u) + b0.w);
+      raw.z = pack2(__uint_as_float(raw.z << 16) + b1.x, __uint_as_float(raw.z & 0xffff0000u) + b1.y);
+      raw.w = pack2(__uint_as_float(raw.w << 16) + b1.z, __uint_as_float(raw.w & 0xffff0000u) + b1.w);
+    }
+    const int page = a.block_table[(size_t)b * a.table_width + pos / a.page_size];
+    bf16* dst = reinterpret_cast<bf16*>(a.v_pages) +
+                (((size_t)page * a.n_v + g) * a.page_size + pos % a.page_size) * a.Dv + piece * 8;
+    *reinterpret_cast<uint4*>(dst) = raw;
+    return;
+  }
+  const int per_tok = a.n_q + a.n_k;
+  const long long total = (long long)a.n_tokens * per_tok;
+  const int vw = lane / P, piece = lane - vw * P;
+  const long long w = warp * vec_per_warp + vw;
+  const bool live_lane = vw < vec_per_warp && w < total;
+  // every lane of a warp walks the same shuffles; lanes without a vector carry zeros
+  int t = 0, vec = 0, b = -1, pos = 0;
+  if (live_lane) {
+    t = (int)(w / per_tok);
+    vec = (int)(w - (long long)t * per_tok);
+    b = a.tok_seq[t];
+    pos = a.tok_pos[t];
+  }
+  const bool is_q = vec < a.n_q;
+  const bool live = live_lane && b >= 0 && (is_q || a.write_cache);
+  const int head = is_q ? vec : vec - a.n_q;
+  const int D = a.Dk;
+  const int col = (is_q ? a.off_q : a.off_k) + head * D + piece * 8;
+  bf16* row = reinterpret_cast<bf16*>(a.buf) + (size_t)t * a.stride;
+  float x[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = 0.f;
+  if (live) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(row + col);
+    const uint32_t wd[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      x[2 * j] = __uint_as_float(wd[j] << 16);
+      x[2 * j + 1] = __uint_as_float(wd[j] & 0xffff0000u);
+    }
+    if (a.bias != nullptr) {
+      const float4 b0 = *reinterpret_cast<const float4*>(a.bias + col), b1 = *reinterpret_cast<const float4*>(a.bias + col + 4);
+      x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w; x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
+    }
+  }
+  const float* weight = is_q ? a.q_weight : a.k_weight;
+  if (a.q_weight != nullptr || a.k_weight != nullptr) {   // the same for the whole launch: no lane leaves the shuffles
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+    float tot = 0.f;
+    for (int j = 0; j < P; ++j) tot += __shfl_sync(0xffffffffu, ss, (vw * P + j) & 31);
+    if (live && weight != nullptr) {
+      const float inv = 1.0f / sqrtf(tot / (float)D + a.eps);
+      const float4 w0 = *reinterpret_cast<const float4*>(weight + piece * 8), w1 = *reinterpret_cast<const float4*>(weight + piece * 8 + 4);
+      x[0] *= inv * w0.x; x[1] *= inv * w0.y; x[2] *= inv * w0.z; x[3] *= inv * w0.w;
+      x[4] *= inv * w1.x; x[5] *= inv * w1.y; x[6] *= inv * w1.z; x[7] *= inv * w1.w;
+    }
+  }
+  if (a.cos_t != nullptr) {
+    const int half = a.n_rot >> 1;
+    const bool turn = live && piece * 8 < a.n_rot;
+    if (a.pairing == 0) {
+      if (turn) {
+        const float* cr = a.cos_t + (size_t)pos * half + piece * 4;
+        const float* sr = a.sin_t + (size_t)pos * half + piece * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (piece * 8 + 2 * j < a.n_rot) {
+            const float u = x[2 * j], v = x[2 * j + 1], c = cr[j], sn = sr[j];
+            x[2 * j] = u * c - v * sn;
+            x[2 * j + 1] = v * c + u * sn;
+          }
+        }
+      }
+    } else {
+      // halves: the partner piece is half / 8 lanes away, on the other side of the middle
+      const int hp = half >> 3;
+      const bool first = piece < hp;
+      const int partner = (vw * P + (first ? piece + hp : piece - hp)) & 31;
+      float p[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) p[j] = __shfl_sync(0xffffffffu, x[j], partner);
+      if (turn) {
+        const int i0 = (first ? piece : piece - hp) * 8;
+        const float* cr = a.cos_t + (size_t)pos * half + i0;
+        const float* sr = a.sin_t + (size_t)pos * half + i0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float c = cr[j], sn = sr[j];
+          x[j] = first ? x[j] * c - p[j] * sn : x[j] * c + p[j] * sn;
+        }
+      }
+    }
+  }
+  if (!live) return;
+  uint4 out;
+  out.x = pack2(x[0], x[1]); out.y = pack2(x[2], x[3]); out.z = pack2(x[4], x[5]); out.w = pack2(x[6], x[7]);
+  if (is_q) {
+    *reinterpret_cast<uint4*>(row + col) = out;
+    return;
+  }
+  const int page = a.block_table[(size_t)b * a.table_width + pos / a.page_size];
+  bf16* dst = reinterpret_cast<bf16*>(a.k_pages) +
+              (((size_t)page * a.n_k + head) * a.page_size + pos % a.page_size) * D + piece * 8;
+  *reinterpret_cast<uint4*>(dst) = out;
 }
 
 struct AttendArgs {
@@ -281,6 +422,16 @@ AB_API int ab_attention_prepare(void* buf, int dtype, int stride, int off_q, int
                 bias};
   const long long warps = (long long)n_tokens * (n_q + n_k + n_v);
   const unsigned blocks = (unsigned)((warps + 3) / 4);
+  const bool pieces = dtype == AB_BF16 && Dk % 8 == 0 && Dv % 8 == 0 && stride % 8 == 0 && off_q % 8 == 0 &&
+                      off_k % 8 == 0 && off_v % 8 == 0 && (n_rot == 0 || pairing == 0 || n_rot % 16 == 0);
+  if (pieces) {
+    const int P = Dk / 8, vpw = 32 / P;
+    const long long qk_warps = ((long long)n_tokens * (n_q + n_k) + vpw - 1) / vpw;
+    const long long v_warps = ((long long)n_tokens * n_v * (Dv / 8) + 31) / 32;
+    ab_launch(attention_prepare_vec_kernel, dim3((unsigned)((qk_warps + v_warps + 3) / 4)), dim3(128), 0, stream, a, P, vpw,
+              qk_warps);
+    return ab_launch_status();
+  }
   if (dtype == AB_F32) ab_launch(attention_prepare_kernel<float>, dim3(blocks), dim3(128), 0, stream, a);
   else if (dtype == AB_BF16) ab_launch(attention_prepare_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, a);
   else return AB_BAD_ARG;

@@ -246,7 +246,7 @@ linattn_stream_kernel(LinAttnArgs a) {
         a.o_raw[((size_t)(tb + tok) * a.H + h) * V + c0 + cc] = sum;
       }
     }
-    // the next round's first barrier comes before `part` and this stage's buffers are written again
+    // the next batch's first barrier comes before `part` and this stage's buffers are written again
   }
   if ((a.mode == 0 ? a.write_state : (a.mode == 1)) && col < V) {
 #pragma unroll
