@@ -29,10 +29,11 @@ MIXERS = {
 
 
 def _check_rot(where: str, rot: dict, dim: int, blended: bool, bad: list) -> None:
-    if not _check_keys(where, rot, {"base": float, "dims": int}, bad):
+    if not _check_keys(where, rot, {"base": float}, bad):
         return
-    if rot["dims"] % 2 or rot["dims"] > dim:
-        bad.append(f"{where}.dims {rot['dims']} must be even and at most dim {dim}")
+    dims = rot.get("dims")
+    if not (_is_int(dims) and dims >= 0 and dims % 2 == 0 and dims <= dim):
+        bad.append(f"{where}.dims {dims!r} must be even and at most dim {dim} (0: no rotation)")
     if not rot["base"] > 0:
         bad.append(f"{where}.base must be positive")
     sc = rot.get("scaling")

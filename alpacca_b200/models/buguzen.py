@@ -46,6 +46,8 @@ def build_buguzen(cfg: BuguzenConfig, opts: BuildOptions) -> DecoderSpec:
     rotations: dict = {}          # layers with the same rotation share one table
 
     def rotation(dim, rot, pairing):
+        if rot["dims"] == 0:          # nothing is rotated
+            return None
         sc = rot.get("scaling") or {}
         key = (dim, rot["dims"], float(rot["base"]), pairing, tuple(sorted(sc.items())))
         if key not in rotations:

@@ -96,6 +96,13 @@ def test_optional_parts_may_be_left_out():
     assert cfg.to_dict()["layers"] == raw["layers"] and "loop" not in cfg.to_dict()
 
 
+def test_a_rotation_over_no_dims_is_no_rotation():
+    raw = copy.deepcopy(bt.TINY_U)
+    raw["layers"][0]["mixer"]["rot"]["dims"] = 0
+    model = build_model(config_from_dict(raw), "float32", "cpu", 64)
+    assert model.spec.layers[0].mixer.position is None and model.spec.layers[2].mixer.position is not None
+
+
 def test_frequency_scaling_of_the_rotation():
     """The package's table of angles against the plain frequencies, for a scaling whose blended range is hit."""
     from alpacca_b200.models.buguzen import _scaling
